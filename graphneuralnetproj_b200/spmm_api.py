@@ -1,0 +1,173 @@
+"""Host-side mirror of the reference's SpMM API over the C boundary of libSpMM_API.so.
+
+Function names and argument order follow the reference header
+(build/SpMM_API.cuh:40-62) and the decompose entry points
+(kernel_benchmark/spmm_decompose.h:12,53).  Everything here is a thin ctypes
+call into the CUDA library; there is no Python or CPU implementation behind it,
+and importing this module fails if the library cannot be built or loaded.
+fp16 host data is carried as numpy float16/uint16 arrays, device data as torch
+tensors (or raw integer device pointers).
+"""
+import ctypes
+
+import numpy as np
+
+from . import build as _build
+
+_u16p = ctypes.POINTER(ctypes.c_uint16)
+_u32p = ctypes.POINTER(ctypes.c_uint32)
+_i32p = ctypes.POINTER(ctypes.c_int)
+
+TILE_M = 128  # rows of an encoded tile (csrc/SpMM_API.cu:249)
+TILE_K = 64   # columns of an encoded tile (csrc/TilingConfig.h:29)
+SUPPORTED_N = (8, 16, 32, 64)  # csrc/SpMM_API.cu:105-196
+
+cudaSuccess = 0
+cudaErrorInvalidValue = 1
+cudaErrorNotSupported = 801
+cudaErrorUnknown = 999
+
+
+def _load():
+    path = _build.build()
+    lib = ctypes.CDLL(path)
+    enc_args = [_u16p, ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.POINTER(_u32p), ctypes.POINTER(_i32p)]
+    lib.spmm_b200_init_sparse_matrix_a.argtypes = enc_args
+    lib.spmm_b200_init_sparse_matrix_a.restype = ctypes.c_int
+    lib.spmm_b200_init_sparse_matrix_a_noreorder.argtypes = enc_args
+    lib.spmm_b200_init_sparse_matrix_a_noreorder.restype = ctypes.c_int
+    lib.spmm_b200_free.argtypes = [ctypes.c_void_p]
+    lib.spmm_b200_free.restype = None
+    lib.spmm_b200_spmm_splitk.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_void_p] + [ctypes.c_void_p] * 2 + \
+        [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
+    lib.spmm_b200_spmm_splitk.restype = ctypes.c_int
+    lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
+    lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
+    for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):
+        f = getattr(lib, name)
+        f.argtypes = [_u16p, _u16p, _u16p, ctypes.c_int]
+        f.restype = None
+    lib.spmm_b200_device_status.argtypes = [ctypes.c_int]
+    lib.spmm_b200_device_status.restype = ctypes.c_int
+    lib.spmm_b200_synth_fp16.argtypes = [_u16p, ctypes.c_long, ctypes.c_uint64, ctypes.c_double, ctypes.c_double]
+    lib.spmm_b200_synth_fp16.restype = None
+    lib.spmm_b200_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_long, _i32p, _i32p, _i32p]
+    lib.spmm_b200_plan.restype = ctypes.c_int
+    lib.GenSparseMatrixBinFile.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p,
+                                           ctypes.c_char_p]
+    lib.GenSparseMatrixBinFile.restype = None
+    return lib
+
+
+LIB = _load()
+LIB_PATH = _build.LIB_PATH
+
+
+def _host_u16(a):
+    a = np.ascontiguousarray(a)
+    if a.dtype == np.float16:
+        a = a.view(np.uint16)
+    if a.dtype != np.uint16:
+        raise TypeError("fp16 host data must be float16 or uint16, got %s" % a.dtype)
+    return a
+
+
+def _encode(fn, A_h, M, N, K):
+    A_h = _host_u16(A_h)
+    if A_h.size != M * K:
+        raise ValueError("A_h has %d elements, expected M*K = %d" % (A_h.size, M * K))
+    wp, op = _u32p(), _i32p()
+    n_offsets = fn(A_h.ctypes.data_as(_u16p), M, N, K, ctypes.byref(wp), ctypes.byref(op))
+    if n_offsets < 0:
+        raise ValueError("M must be a positive multiple of %d and K of %d (got M=%d, K=%d)" % (TILE_M, TILE_K, M, K))
+    offsets = np.ctypeslib.as_array(op, shape=(n_offsets,)).copy()
+    n_words = int(offsets[-1]) * 4
+    words = np.ctypeslib.as_array(wp, shape=(max(n_words, 1),))[:n_words].copy()
+    LIB.spmm_b200_free(ctypes.cast(wp, ctypes.c_void_p))
+    LIB.spmm_b200_free(ctypes.cast(op, ctypes.c_void_p))
+    return words, offsets, n_offsets
+
+
+def InitSparseMatrixA_API(A_h, M, N, K):
+    """Dense host A[M][K] -> (Compressed_A uint32 words, TileOffsets int32, NumOffsets).
+
+    Same output as the reference's InitSparseMatrixA_API (csrc/SpMM_API.cu:241-438);
+    NumOffsets is its return value and 4 * TileOffsets[-1] the word count."""
+    return _encode(LIB.spmm_b200_init_sparse_matrix_a, A_h, M, N, K)
+
+
+def InitSparseMatrixA_API_NoReorder(A_h, M, N, K):
+    """Scan-order variant (csrc/SpMM_API.cu:441-567)."""
+    return _encode(LIB.spmm_b200_init_sparse_matrix_a_noreorder, A_h, M, N, K)
+
+
+def _dev_ptr(x):
+    if x is None:
+        return None
+    if isinstance(x, int):
+        return ctypes.c_void_p(x)
+    if not x.is_cuda:
+        raise ValueError("expected a CUDA tensor")
+    if not x.is_contiguous():
+        raise ValueError("expected a contiguous tensor")
+    return ctypes.c_void_p(x.data_ptr())
+
+
+def SpMM_SplitK_API(stream, A, Compressed_A, A1_Ind_data, metadata, TileOffsets, B, C, M_Global, N_Global, K_Global,
+                    Reduction_Workspace, Split_K):
+    """C[M][N] = A_sparse * B on `stream` (a torch.cuda.Stream, a raw handle, or None for the current stream).
+
+    Argument order and meaning as in the reference (build/SpMM_API.cuh:40-52).
+    Returns the cudaError_t of the launch as an int (0 = success); asynchronous."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    handle = stream if isinstance(stream, int) else stream.cuda_stream
+    return LIB.spmm_b200_spmm_splitk(ctypes.c_void_p(handle), _dev_ptr(A), _dev_ptr(Compressed_A), _dev_ptr(A1_Ind_data),
+                                     _dev_ptr(metadata), _dev_ptr(TileOffsets), _dev_ptr(B), _dev_ptr(C), M_Global,
+                                     N_Global, K_Global, _dev_ptr(Reduction_Workspace), Split_K)
+
+
+def workspace_bytes(M_Global, N_Global, Split_K):
+    """The reference's workspace contract: Split_K * M * N * sizeof(half) (build/SpMM_API.cuh:34-38)."""
+    return int(LIB.spmm_b200_workspace_bytes(M_Global, N_Global, Split_K))
+
+
+def decompose(A, v1=False):
+    """2:4 part + residual (kernel_benchmark/spmm_decompose.h:12-51, v1 :53-142). Returns (A1, A2) as uint16 bits."""
+    A = _host_u16(A)
+    flat = A.reshape(-1)
+    if flat.size % 4:
+        raise ValueError("length must be a multiple of 4")
+    A1 = np.empty_like(flat)
+    A2 = np.empty_like(flat)
+    fn = LIB.spmm_b200_decompose_v1 if v1 else LIB.spmm_b200_decompose
+    fn(flat.ctypes.data_as(_u16p), A1.ctypes.data_as(_u16p), A2.ctypes.data_as(_u16p), flat.size)
+    return A1.reshape(A.shape), A2.reshape(A.shape)
+
+
+def GenSparseMatrixBinFile(dense_path, M, K, nz_path, offsets_path, sizes_path):
+    """File front end used by the weight-conversion tools (csrc/SpMM_API.cu:1565-1620)."""
+    LIB.GenSparseMatrixBinFile(dense_path.encode(), M, K, nz_path.encode(), offsets_path.encode(), sizes_path.encode())
+
+
+def device_status(reset=False):
+    """0 if no kernel on the current device ever abandoned a wait; synchronises the device."""
+    return int(LIB.spmm_b200_device_status(1 if reset else 0))
+
+
+def synth_fp16(shape, seed, sigma, p_zero=0.0):
+    """Seeded synthetic fp16 data (uint16 bits): sigma * N(0,1), zeroed with probability p_zero."""
+    out = np.empty(shape, np.uint16)
+    LIB.spmm_b200_synth_fp16(out.ctypes.data_as(_u16p), out.size, seed, float(sigma), float(p_zero))
+    return out
+
+
+def plan(tiles_m, tiles_k, max_ctas, slots_avail):
+    """The kernel's work partition: (chunk_begin[ctas+1], split_rows_above[ctas], slots_used)."""
+    cb = np.zeros(320, np.int32)
+    ab = np.zeros(320, np.int32)
+    used = ctypes.c_int(0)
+    n = LIB.spmm_b200_plan(tiles_m, tiles_k, max_ctas, slots_avail, cb.ctypes.data_as(_i32p), ab.ctypes.data_as(_i32p),
+                           ctypes.byref(used))
+    return cb[:n + 1].copy(), ab[:n].copy(), used.value

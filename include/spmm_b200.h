@@ -1,0 +1,84 @@
+/* Plain-C boundary of libSpMM_API.so (sm_100a).
+ *
+ * The reference exports its entry points with C++ linkage
+ * (build/SpMM_API.cuh:40-96); SpMM_API.cuh in this directory keeps those
+ * symbols for callers that link C++.  The functions below are thin extern "C"
+ * views of the same entry points for foreign-function interfaces (Python
+ * ctypes, cgo, JNI ...).  fp16 data is passed as raw 16-bit patterns, streams
+ * as the cudaStream_t handle cast to void*, and device pointers as void*.
+ * Functions returning int return a cudaError_t value unless stated otherwise.
+ */
+#ifndef SPMM_B200_H
+#define SPMM_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* InitSparseMatrixA_API, build/SpMM_API.cuh:55 (csrc/SpMM_API.cu:241-438).
+ * Host dense A[M][K] -> tiled-CSL words + offsets (malloc'd, release with
+ * spmm_b200_free).  Returns the number of offsets (tiles + 2), or -1 if M is
+ * not a multiple of 128 or K of 64 (the C++ symbol aborts there, like the
+ * reference's assert). */
+int spmm_b200_init_sparse_matrix_a(const uint16_t* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets);
+
+/* InitSparseMatrixA_API_NoReorder, build/SpMM_API.cuh:57-62 (csrc/SpMM_API.cu:441-567). */
+int spmm_b200_init_sparse_matrix_a_noreorder(
+    const uint16_t* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets);
+
+/* free() for buffers returned by the encoders (the reference's callers call free directly,
+ * kernel_benchmark/spmm_test.cu:348-349). */
+void spmm_b200_free(void* p);
+
+/* SpMM_SplitK_API, build/SpMM_API.cuh:40-52 (csrc/SpMM_API.cu:79-208).  Same
+ * argument order and meaning; all pointers are device pointers. */
+int spmm_b200_spmm_splitk(void*       stream,
+                          const void* A,
+                          const void* Compressed_A,
+                          const void* A1_Ind_data,
+                          const void* metadata,
+                          const int*  TileOffsets,
+                          const void* B,
+                          void*       C,
+                          int         M_Global,
+                          int         N_Global,
+                          int         K_Global,
+                          void*       Reduction_Workspace,
+                          int         Split_K);
+
+/* The reference's workspace contract, build/SpMM_API.cuh:34-38:
+ * Split_K * M * N * sizeof(half) bytes. */
+size_t spmm_b200_workspace_bytes(int M_Global, int N_Global, int Split_K);
+
+/* decompose / decompose_v1, kernel_benchmark/spmm_decompose.h:12-51 and :53-142:
+ * split A into a 2:4-compliant part A1 and the residual A2 (both dense, length
+ * elements, caller-allocated). */
+void spmm_b200_decompose(const uint16_t* A, uint16_t* A1, uint16_t* A2, int length);
+void spmm_b200_decompose_v1(const uint16_t* A, uint16_t* A1, uint16_t* A2, int length);
+
+/* Device-side status of the current device: 0 = ok, 1 = a bounded wait inside a
+ * kernel gave up.  Synchronises the device.  With reset != 0 the status and the
+ * arrival counters are cleared afterwards.  No counterpart in the reference,
+ * whose kernels cannot report anything. */
+int spmm_b200_device_status(int reset);
+
+/* Seeded synthetic inputs (stand-ins for pruned model weights and
+ * activations): element i of the stream is drawn from a counter-based
+ * splitmix64 generator, value = fp16(sigma * gaussian), zeroed with
+ * probability p_zero.  No counterpart in the reference, whose harness uses
+ * rand() (kernel_benchmark/spmm_test_utils.h:108-162). */
+void spmm_b200_synth_fp16(uint16_t* out, long count, uint64_t seed, double sigma, double p_zero);
+
+/* The work partition the SpMM kernel would use (for tests of the host logic):
+ * fills chunk_begin[0..ctas] and split_rows_above[0..ctas-1], returns the
+ * number of thread blocks; *slots_used gets the number of workspace slots. */
+int spmm_b200_plan(int tiles_m, int tiles_k, int max_ctas, long slots_avail, int* chunk_begin, int* split_rows_above,
+                   int* slots_used);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

@@ -1,0 +1,47 @@
+"""The shared library loads without a GPU and exports every symbol the headers declare."""
+import ctypes
+import os
+import re
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+# Itanium-mangled names of the C++ declarations in include/SpMM_API.cuh; identical to the
+# symbols of the reference's library so that its callers link unchanged.
+CXX_SYMBOLS = [
+    "_Z15SpMM_SplitK_APIP11CUstream_stPK6__halfPK5uint4PKmPKiSA_S3_PS1_iiiSB_i",
+    "_Z21InitSparseMatrixA_APIP6__halfiiiPPjPPi",
+    "_Z31InitSparseMatrixA_API_NoReorderP6__halfiiiPPjPPi",
+]
+
+
+def declared_c_symbols():
+    names = set()
+    for header in ("spmm_b200.h", "SpMM_API.cuh"):
+        text = open(os.path.join(ROOT, "include", header)).read()
+        text = re.sub(r"/\*.*?\*/", "", text, flags=re.S)
+        text = re.sub(r"//[^\n]*", "", text)
+        names |= set(re.findall(r"\b(spmm_b200_\w+)\s*\(", text))
+        names |= set(re.findall(r'extern "C" \w+ (\w+)\(', text))
+    return sorted(names)
+
+
+def test_library_exports_declared_symbols(sp):
+    lib = ctypes.CDLL(sp.LIB_PATH)
+    declared = declared_c_symbols()
+    assert "spmm_b200_spmm_splitk" in declared and "GenSparseMatrixBinFile" in declared
+    for name in declared + CXX_SYMBOLS:
+        assert hasattr(lib, name), "missing export: " + name
+
+
+def test_reference_symbol_names_match(oracle):
+    """Where the compiled reference is present, its exported encoder / SpMM symbols exist under the same names."""
+    import pytest
+    if not oracle.have_ref():
+        pytest.skip("compiled reference not present")
+    ref = oracle.ref()
+    for name in CXX_SYMBOLS + ["GenSparseMatrixBinFile"]:
+        assert hasattr(ref, name)
+
+
+def test_workspace_contract(sp):
+    assert sp.workspace_bytes(7168, 16, 5) == 5 * 7168 * 16 * 2
