@@ -58,30 +58,46 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity)
     return done != 0;
 }
 
-// Bounded wait.  Spins on the barrier; after a short burst it also watches a
-// block-wide abort word and a wall-clock deadline.  Returns false if the wait
-// was abandoned, in which case *abort_word has been set so that every other
-// role in the block gives up as well.
+// try_wait that lets the hardware park the thread for up to `suspend_ns` while the phase is
+// pending, so that a waiting warp does not compete for issue slots.
+__device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t parity, uint32_t suspend_ns)
+{
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity), "r"(suspend_ns)
+                 : "memory");
+    return done != 0;
+}
+
+// Bounded wait.  Each poll may park the thread for up to kSuspendNs; between polls the
+// block-wide abort word is checked, and every 256 polls a wall-clock deadline.  Returns
+// false if the wait was abandoned, in which case *abort_word has been set so that every
+// other role in the block gives up as well.
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
+constexpr uint32_t kSuspendNs   = 20000u;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word)
 {
+    if (mbar_try_wait(bar, parity))
+        return true;
+    uint64_t start = 0;
 #pragma unroll 1
-    for (int i = 0; i < 4096; i++)
-        if (mbar_try_wait(bar, parity))
+    for (uint32_t polls = 0;; polls++) {
+        if (mbar_try_wait_suspend(bar, parity, kSuspendNs))
             return true;
-    const uint64_t start = global_timer_ns();
-#pragma unroll 1
-    for (;;) {
-#pragma unroll 1
-        for (int i = 0; i < 256; i++)
-            if (mbar_try_wait(bar, parity))
-                return true;
         if (*abort_word != 0)
             return false;
-        if (global_timer_ns() - start > kWaitLimitNs) {
-            *abort_word = 1;
-            return false;
+        if ((polls & 255u) == 0) {
+            const uint64_t now = global_timer_ns();
+            if (start == 0)
+                start = now;
+            else if (now - start > kWaitLimitNs) {
+                *abort_word = 1;
+                return false;
+            }
         }
     }
 }
@@ -122,6 +138,33 @@ __device__ __forceinline__ uint4 ld_stream_128(const uint4* p)
 __device__ __forceinline__ void st_shared_u16(uint32_t addr, uint32_t value)
 {
     asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(static_cast<uint16_t>(value)) : "memory");
+}
+
+// Scatter of one 4-word vector of tiled-CSL words: each word is value (low half) | position
+// (high half); the value goes to half-word `position` of the tile at shared address `tile`.
+__device__ __forceinline__ void scatter_words(uint32_t tile, const uint4& w)
+{
+    asm volatile("{\n\t"
+                 ".reg .b16 v0, v1, v2, v3, p0, p1, p2, p3;\n\t"
+                 ".reg .b32 a0, a1, a2, a3;\n\t"
+                 "mov.b32 {v0, p0}, %1;\n\t"
+                 "mov.b32 {v1, p1}, %2;\n\t"
+                 "mov.b32 {v2, p2}, %3;\n\t"
+                 "mov.b32 {v3, p3}, %4;\n\t"
+                 "mad.wide.u16 a0, p0, 2, %0;\n\t"
+                 "mad.wide.u16 a1, p1, 2, %0;\n\t"
+                 "mad.wide.u16 a2, p2, 2, %0;\n\t"
+                 "mad.wide.u16 a3, p3, 2, %0;\n\t"
+                 "st.shared.b16 [a0], v0;\n\t"
+                 "st.shared.b16 [a1], v1;\n\t"
+                 "st.shared.b16 [a2], v2;\n\t"
+                 "st.shared.b16 [a3], v3;\n\t"
+                 "}" ::"r"(tile),
+                 "r"(w.x),
+                 "r"(w.y),
+                 "r"(w.z),
+                 "r"(w.w)
+                 : "memory");
 }
 
 __device__ __forceinline__ void st_shared_zero_128(uint32_t addr)

@@ -14,13 +14,15 @@
 namespace spmm_b200 {
 namespace {
 
-// Decoder warps = depth of the A/B tile ring, bounded by 227 KB of shared memory per block.
+// Ring depth D (bounded by 227 KB of shared memory per block), decoder warps per ring slot and
+// 4-word vectors held per lane; WPT * VPL * 32 vectors (7168 bytes of words) are in flight per slot.
 template<int N>
-constexpr int decode_warps()
-{
-    return N <= 32 ? 10 : 8;
-}
-constexpr int kVectorsPerLane = 14;  // 14 * 32 vectors = 7168 bytes of words in flight per decoder warp
+struct DecodeConfig {
+    static constexpr int D   = N <= 32 ? 8 : 6;
+    static constexpr int Q   = N <= 32 ? 4 : 3;  // MMA-issuing warps
+    static constexpr int WPT = 1;
+    static constexpr int VPL = 14;
+};
 
 struct DeviceInfo {
     int  sm_count = 0;
@@ -65,13 +67,59 @@ const Schedule& cached_schedule(const PlanKey& key)
     return plans[slot];
 }
 
+#ifdef SPMM_B200_ABLATIONS
+template<int D, int Q, int WPT, int ABL>
+cudaError_t launch_ablated(cudaStream_t stream, const DecodeParams& params)
+{
+    constexpr int smem = decode_smem_bytes<16, D>();
+    auto kern = spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    kern<<<params.sched.num_ctas, decode_threads<D, Q, WPT>(), smem, stream>>>(params);
+    return cudaGetLastError();
+}
+template<int D, int Q, int WPT>
+cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, int abl)
+{
+    switch (abl) {
+        case 1: return launch_ablated<D, Q, WPT, 1>(stream, params);
+        case 2: return launch_ablated<D, Q, WPT, 2>(stream, params);
+        case 3: return launch_ablated<D, Q, WPT, 3>(stream, params);
+        case 4: return launch_ablated<D, Q, WPT, 4>(stream, params);
+        case 12: return launch_ablated<D, Q, WPT, 12>(stream, params);
+        case 9: return launch_ablated<D, Q, WPT, 9>(stream, params);
+        case 10: return launch_ablated<D, Q, WPT, 10>(stream, params);
+        case 8: return launch_ablated<D, Q, WPT, 8>(stream, params);
+        case 11: return launch_ablated<D, Q, WPT, 11>(stream, params);
+        case 31: return launch_ablated<D, Q, WPT, 31>(stream, params);
+        default: return launch_ablated<D, Q, WPT, 0>(stream, params);
+    }
+}
+#endif
+
 template<int N>
 cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, const DecodeParams& params)
 {
+#ifdef SPMM_B200_ABLATIONS
+    if (N == 16) {
+        const char* env = getenv("SPMM_B200_ABLATE");
+        const char* envd = getenv("SPMM_B200_D");
+        const int abl = env ? atoi(env) : 0;
+        switch (envd ? atoi(envd) : 842) {   // D * 100 + Q * 10 + WPT
+            case 841: return launch_ablated_d<8, 4, 1>(stream, params, abl);
+            case 822: return launch_ablated_d<8, 2, 2>(stream, params, abl);
+            case 1022: return launch_ablated_d<10, 2, 2>(stream, params, abl);
+            case 1052: return launch_ablated_d<10, 5, 2>(stream, params, abl);
+            case 932: return launch_ablated_d<9, 3, 2>(stream, params, abl);
+            case 812: return launch_ablated_d<8, 1, 2>(stream, params, abl);
+            default: return launch_ablated_d<8, 4, 2>(stream, params, abl);
+        }
+    }
+#endif
     constexpr int NB   = N < 16 ? 16 : N;
-    constexpr int D    = decode_warps<N>();
+    using Cfg          = DecodeConfig<N>;
+    constexpr int D    = Cfg::D;
     constexpr int smem = decode_smem_bytes<NB, D>();
-    auto          kern = spmm_decode_kernel<N, D, kVectorsPerLane>;
+    auto          kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -80,7 +128,7 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
         }
         dev.attrs_set[n_index] = true;
     }
-    kern<<<params.sched.num_ctas, (kFirstDecodeWarp + D) * 32, smem, stream>>>(params);
+    kern<<<params.sched.num_ctas, decode_threads<D, Cfg::Q, Cfg::WPT>(), smem, stream>>>(params);
     return cudaGetLastError();
 }
 
@@ -156,6 +204,18 @@ cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
 
 // ------------------------------------------------------------------ extern "C"
 extern "C" {
+#ifdef SPMM_B200_ABLATIONS
+int spmm_b200_debug_trace(unsigned long long* out)
+{
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, spmm_b200::g_trace, sizeof(unsigned long long) * 320 * 16);
+}
+int spmm_b200_debug_fine(long long* out)
+{
+    cudaDeviceSynchronize();
+    return (int)cudaMemcpyFromSymbol(out, spmm_b200::g_fine, sizeof(long long) * 320 * 32);
+}
+#endif
 
 int spmm_b200_init_sparse_matrix_a(const uint16_t* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets)
 {

@@ -8,14 +8,25 @@
 // One persistent thread block per SM works through a contiguous chunk of the
 // tile sequence (see schedule.h).  Roles, by warp:
 //
-//   warps 0..3     epilogue: TMEM -> registers -> C, or -> an fp32 slot plus the
-//                  last-arriver reduction for rows whose K range is shared
-//   warp  4        allocates TMEM; one lane issues tcgen05.mma and commits
-//   warps 5..5+D-1 decoders, one 128 x 64 tile at a time each, round-robin:
-//                  128-bit streaming loads of the tile's words into registers,
-//                  zero the warp's own 16 KB A buffer, scatter the values to
-//                  the half-word positions the words carry, stage the matching
-//                  64 x N slice of B, hand the pair to the MMA lane
+//   warps 0..3   epilogue: TMEM -> registers -> C, or -> an fp32 slot plus the
+//                last-arriver reduction for rows whose K range is shared
+//   warps 4..4+Q-1  MMA issue: one lane each; warp q takes tiles q, q + Q, ... of the
+//                chunk and accumulates them in its own TMEM accumulator (the
+//                epilogue adds the Q accumulators in a fixed order).  Several
+//                issuers because one lane, sharing its scheduler with busy
+//                decoder warps, cannot issue four MMAs and a commit per tile fast
+//                enough; warp 4 also allocates TMEM
+//   warps 4+Q..  decoders.  The block keeps a ring of D tile buffers (16 KB of
+//                restored A plus two staged B slices each); buffer s is owned by
+//                a team of WPT warps that handles tiles s, s + D, s + 2D, ... of
+//                the chunk.  Per tile a team
+//                  - streams the tile's words into registers with 128-bit loads
+//                    (issued one tile ahead, right after the previous scatter),
+//                  - waits until the tensor core has finished with the buffer,
+//                  - clears the buffer with 128-bit stores,
+//                  - scatters the values to the half-word positions the words carry,
+//                  - issues the copy of its next tile's B slice, and hands the
+//                    buffer to an MMA lane.
 //
 // The position stored in each word, row * 64 + (col ^ ((row % 8) << 3))
 // (csrc/SpMM_API.cu:330-339), is the element offset of (row, col) in a K-major
@@ -38,12 +49,11 @@
 
 namespace spmm_b200 {
 
-constexpr int kTileRows        = 128;    // rows of an encoded tile = UMMA M
-constexpr int kTileCols        = 64;     // k extent of an encoded tile
+constexpr int kTileRows        = 128;  // rows of an encoded tile = UMMA M
+constexpr int kTileCols        = 64;   // k extent of an encoded tile
 constexpr int kATileBytes      = kTileRows * kTileCols * 2;
 constexpr int kEpilogueWarps   = 4;
-constexpr int kMmaWarp         = 4;
-constexpr int kFirstDecodeWarp = 5;
+constexpr int kFirstMmaWarp    = 4;
 constexpr int kMaxRowTiles     = 8192;  // arrival counters are sized for M <= 128 * 8192
 
 enum DeviceStatus : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
@@ -53,6 +63,22 @@ enum DeviceStatus : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
 // last arriver resets its counter.
 __device__ unsigned int g_row_arrivals[kMaxRowTiles * kEpilogueWarps];
 __device__ int          g_device_status;
+
+#ifdef SPMM_B200_ABLATIONS
+__device__ unsigned long long g_trace[320 * 16];
+__device__ long long          g_fine[320 * 32];
+__device__ __forceinline__ long long fine_clock()
+{
+    long long c;
+    asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
+    return c;
+}
+#define SPMM_TRACE(slot) do { if (lane == 0) g_trace[blockIdx.x * 16 + (slot)] = ptx::global_timer_ns(); } while (0)
+#define SPMM_FINE(cond, slot) do { if ((cond) && lane == 0) g_fine[blockIdx.x * 32 + (slot)] = fine_clock(); } while (0)
+#else
+#define SPMM_TRACE(slot) do { } while (0)
+#define SPMM_FINE(cond, slot) do { } while (0)
+#endif
 
 struct DecodeParams {
     const uint4* words;         // tiled-CSL words, viewed as 4-word vectors
@@ -83,13 +109,40 @@ struct BTile {
 template<int NB, int D>
 constexpr int decode_smem_bytes()
 {
-    return 1024 + D * (kATileBytes + BTile<NB>::kBytes) + 256;
+    return 1024 + D * (kATileBytes + 2 * BTile<NB>::kBytes) + 256;  // per ring slot: one A buffer, two B buffers
 }
 
-// N  : columns of B / C (8, 16, 32, 64);   NB : columns of the staged B tile (16 when N == 8)
-// D  : decoder warps = depth of the A/B tile ring;   VPL : 4-word vectors held per lane
-template<int N, int D, int VPL>
-__global__ void __launch_bounds__((kFirstDecodeWarp + D) * 32, 1)
+template<int D, int Q, int WPT>
+constexpr int decode_threads()
+{
+    return (kFirstMmaWarp + Q + D * WPT) * 32;
+}
+
+// TMEM is allocated in powers of two, at least 32 columns.
+__host__ __device__ constexpr uint32_t tmem_columns(uint32_t needed)
+{
+    uint32_t c = 32;
+    while (c < needed)
+        c *= 2;
+    return c;
+}
+
+// Lane 0 polls, the warp follows.  Returns false (warp-uniform) when the wait was abandoned.
+__device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatile int* abort_word, int lane)
+{
+    int ok = 1;
+    if (lane == 0)
+        ok = ptx::mbar_wait_bounded(bar, parity, abort_word) ? 1 : 0;
+    return __shfl_sync(0xffffffffu, ok, 0) != 0;
+}
+
+// N   : columns of B / C (8, 16, 32, 64);   NB : columns of the staged B tile (16 when N == 8)
+// D   : depth of the tile ring;  Q : MMA-issuing warps;  WPT : decoder warps per ring slot;
+// VPL : 4-word vectors held per lane
+// ABL : debugging ablation mask (0 in production): 1 no clearing, 2 no scatter, 4 no word loads,
+//       8 no MMA, 16 no B copy
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0>
+__global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
     constexpr int NB = N < 16 ? 16 : N;
@@ -98,7 +151,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base    = smem_base;
     const uint32_t b_base    = a_base + D * kATileBytes;
-    const uint32_t bar_base  = b_base + D * BT::kBytes;
+    const uint32_t bar_base  = b_base + 2 * D * BT::kBytes;
     // barrier map (8 bytes each): [0,D) tile full, [D,2D) tile free, then acc full x2, acc free x2
     auto tile_full = [&](int s) { return bar_base + 8u * s; };
     auto tile_free = [&](int s) { return bar_base + 8u * (D + s); };
@@ -117,26 +170,28 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const int tile_end   = p.sched.chunk_begin[cta + 1];
     const int num_tiles  = tile_end - tile_begin;
     const int tiles_k    = p.tiles_k;
-    constexpr uint32_t kTmemCols = 2 * NB < 32 ? 32 : 2 * NB;
+    constexpr int      kFirstDecodeWarp = kFirstMmaWarp + Q;
+    constexpr uint32_t kTmemCols        = tmem_columns(2 * Q * NB);  // accumulator (q, b) at column (b * Q + q) * NB
+    static_assert(2 * Q * NB <= 512, "accumulators exceed the 512 TMEM columns");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < D; s++) {
-            ptx::mbar_init(tile_full(s), 1);
+            ptx::mbar_init(tile_full(s), WPT);
             ptx::mbar_init(tile_free(s), 1);
         }
         for (int b = 0; b < 2; b++) {
-            ptx::mbar_init(acc_full(b), 1);
+            ptx::mbar_init(acc_full(b), Q);
             ptx::mbar_init(acc_free(b), kEpilogueWarps);
         }
         *abort_word = 0;
         ptx::mbar_init_fence();
     }
-    if (N < NB) {
-        // Columns N..NB-1 of the staged B tiles are never written; clear them once.
-        for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(D * BT::kBytes); off += blockDim.x * 16u)
-            ptx::st_shared_zero_128(b_base + off);
-    }
-    if (warp == kMmaWarp) {
+    // Clear the ring once: A buffers are kept all-zero between tiles, and columns N..NB-1 of the
+    // staged B slices (N == 8) are never written.
+    for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(D * (kATileBytes + 2 * BT::kBytes));
+         off += blockDim.x * 16u)
+        ptx::st_shared_zero_128(a_base + off);
+    if (warp == kFirstMmaWarp) {
         ptx::tmem_alloc(tmem_slot_addr, kTmemCols);
         ptx::tmem_relinquish();
     }
@@ -144,105 +199,187 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
+    if (warp == 0)
+        SPMM_TRACE(0);  // prologue done
 
     if (warp >= kFirstDecodeWarp) {
-        // ------------------------------------------------------------ decoder
-        const int      w      = warp - kFirstDecodeWarp;
-        const uint32_t a_tile = a_base + w * kATileBytes;
-        const uint32_t b_tile = b_base + w * BT::kBytes;
-        int off0 = 0, off1 = 0;
-        if (w < num_tiles) {
-            off0 = __ldg(p.tile_offsets + tile_begin + w);
-            off1 = __ldg(p.tile_offsets + tile_begin + w + 1);
+        // ------------------------------------------------------------ decoder team
+        const int      s_own  = (warp - kFirstDecodeWarp) / WPT;  // ring slot of this team
+        const int      h      = (warp - kFirstDecodeWarp) % WPT;  // this warp's share of the tile
+        const uint32_t a_tile = a_base + s_own * kATileBytes;
+        auto team_sync = [&]() {
+            if (WPT > 1)
+                asm volatile("bar.sync %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
+            else
+                __syncwarp();
+        };
+        // B staging: a 64 x N slice is kTileCols * N / 8 chunks of 16 bytes, contiguous in global
+        // memory; this warp copies chunks first_chunk, first_chunk + WPT * 32, ...  Chunk c lands at
+        // swizzle(row * row_bytes + col * 16) with row = c / chunks_per_row, col = c % chunks_per_row.
+        constexpr int kChunksPerRow = N / 8;
+        constexpr int kChunks       = kTileCols * kChunksPerRow;
+        const int     first_chunk   = h * 32 + lane;
+        auto stage_b = [&](int j, int parity) {
+            if (ABL & 16)
+                return;
+            const uint4*   b_src = reinterpret_cast<const uint4*>(p.B) + static_cast<size_t>(j) * kChunks + first_chunk;
+            const uint32_t dst   = b_base + (parity * D + s_own) * BT::kBytes;
+#pragma unroll
+            for (int i = 0; i < kChunks / (WPT * 32); i++) {
+                const uint32_t c   = first_chunk + i * WPT * 32;
+                const uint32_t row = c / kChunksPerRow, col = c % kChunksPerRow;
+                ptx::cp_async_16(dst + BT::swizzle(row * BT::kRowBytes + col * 16u), b_src + i * WPT * 32);
+            }
+        };
+        auto zero_a = [&]() {
+#pragma unroll
+            for (int i = h; i < kATileBytes / (32 * 16); i += WPT)
+                ptx::st_shared_zero_128(a_tile + lane * 16u + i * 512u);
+        };
+        // Vector v of this lane within a tile: teams interleave their warps by groups of 32 vectors.
+        const int lane_vec = h * 32 + lane;
+        uint4     r[VPL];  // this warp's share of the tile's words
+        int       nvec = 0, next0 = 0, next1 = 0;
+        int       j    = (tile_begin + s_own) % tiles_k;
+        auto load_words = [&](const uint4* from, int count) {
+#pragma unroll
+            for (int v = 0; v < VPL; v++)
+                if (lane_vec + v * WPT * 32 < count) {
+                    if (ABL & 4)
+                        r[v] = make_uint4(lane << 17, (lane + 32) << 17, (lane + 64) << 17, (lane + 96) << 17);
+                    else
+                        r[v] = ptx::ld_stream_128(from + v * WPT * 32);
+                }
+        };
+        const uint4* src = p.words + lane_vec;  // always offset by this lane's first vector
+        if (s_own < num_tiles) {
+            const int off0 = __ldg(p.tile_offsets + tile_begin + s_own);
+            const int off1 = __ldg(p.tile_offsets + tile_begin + s_own + 1);
+            nvec           = off1 - off0;
+            src            = p.words + off0 + lane_vec;
+            load_words(src, nvec);
+            stage_b(j, 0);
+            if (s_own + D < num_tiles) {
+                next0 = __ldg(p.tile_offsets + tile_begin + s_own + D);
+                next1 = __ldg(p.tile_offsets + tile_begin + s_own + D + 1);
+            }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        if (s_own == 0 && h == 0)
+            SPMM_TRACE(1);  // first loads issued
         int use = 0;
 #pragma unroll 1
-        for (int l = w; l < num_tiles; l += D, ++use) {
-            const int    t    = tile_begin + l;
-            const int    nvec = off1 - off0;
-            const uint4* src  = p.words + off0;
-            uint4        r[VPL];
-#pragma unroll
-            for (int v = 0; v < VPL; v++)
-                if (v * 32 + lane < nvec)
-                    r[v] = ptx::ld_stream_128(src + v * 32 + lane);
-            if (l + D < num_tiles) {
-                off0 = __ldg(p.tile_offsets + t + D);
-                off1 = __ldg(p.tile_offsets + t + D + 1);
-            }
-            if (use > 0 && !ptx::mbar_wait_bounded(tile_free(w), (use - 1) & 1, abort_word))
-                break;
-            // B slice of this k tile: 64 rows of N halves, contiguous in global memory.
-            {
-                const uint4* b_src = reinterpret_cast<const uint4*>(p.B + static_cast<size_t>(t % tiles_k) * kTileCols * N);
-                constexpr int kChunksPerRow = N / 8;
-#pragma unroll
-                for (int c = lane; c < kTileCols * kChunksPerRow; c += 32) {
-                    const uint32_t row = c / kChunksPerRow, col = c % kChunksPerRow;
-                    ptx::cp_async_16(b_tile + BT::swizzle(row * BT::kRowBytes + col * 16u), b_src + c);
+        for (int l = s_own; l < num_tiles; l += D, ++use) {
+            const bool has_next = l + D < num_tiles;
+            const bool fine     = (s_own == 0 && h == 0 && use == 8);
+            SPMM_FINE(fine, 0);
+            if (use > 0) {
+                if (!ptx::mbar_wait_bounded(tile_free(s_own), (use - 1) & 1, abort_word)) {
+                    // A team mate that saw the barrier complete may be waiting at the team barrier below.
+                    if (WPT > 1)
+                        asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
+                    break;
                 }
+                SPMM_FINE(fine, 7);
+                if (!(ABL & 1))
+                    zero_a();
+                team_sync();  // the whole buffer is clear before anyone scatters into it
             }
+            SPMM_FINE(fine, 1);
+            // The B buffer of the other parity was last read by the tile whose completion was just observed.
+            int j_next = j + D;
+            while (j_next >= tiles_k)
+                j_next -= tiles_k;
+            if (has_next)
+                stage_b(j_next, (use + 1) & 1);
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            SPMM_FINE(fine, 2);
+            if (!(ABL & 2)) {
 #pragma unroll
-            for (int i = 0; i < kATileBytes / (32 * 16); i++)
-                ptx::st_shared_zero_128(a_tile + (i * 32 + lane) * 16u);
-            __syncwarp();
-#pragma unroll
-            for (int v = 0; v < VPL; v++)
-                if (v * 32 + lane < nvec) {
-                    ptx::st_shared_u16(a_tile + ((r[v].x >> 16) << 1), r[v].x);
-                    ptx::st_shared_u16(a_tile + ((r[v].y >> 16) << 1), r[v].y);
-                    ptx::st_shared_u16(a_tile + ((r[v].z >> 16) << 1), r[v].z);
-                    ptx::st_shared_u16(a_tile + ((r[v].w >> 16) << 1), r[v].w);
-                }
+                for (int v = 0; v < VPL; v++)
+                    if (lane_vec + v * WPT * 32 < nvec)
+                        ptx::scatter_words(a_tile, r[v]);
+            }
+            if (nvec > VPL * WPT * 32) {  // denser than the register budget: stream the rest
 #pragma unroll 1
-            for (int idx = VPL * 32 + lane; idx < nvec; idx += 32) {  // tiles denser than VPL * 32 vectors
-                const uint4 x = ptx::ld_stream_128(src + idx);
-                ptx::st_shared_u16(a_tile + ((x.x >> 16) << 1), x.x);
-                ptx::st_shared_u16(a_tile + ((x.y >> 16) << 1), x.y);
-                ptx::st_shared_u16(a_tile + ((x.z >> 16) << 1), x.z);
-                ptx::st_shared_u16(a_tile + ((x.w >> 16) << 1), x.w);
+                for (int idx = lane_vec + VPL * WPT * 32; idx < nvec; idx += WPT * 32)
+                    ptx::scatter_words(a_tile, ptx::ld_stream_128(src - lane_vec + idx));
             }
-            ptx::cp_async_wait_all();
+            SPMM_FINE(fine, 3);
+            if (has_next) {
+                nvec = next1 - next0;
+                src  = p.words + next0 + lane_vec;
+                load_words(src, nvec);
+                if (l + 2 * D < num_tiles) {
+                    next0 = __ldg(p.tile_offsets + tile_begin + l + 2 * D);
+                    next1 = __ldg(p.tile_offsets + tile_begin + l + 2 * D + 1);
+                }
+            }
+            SPMM_FINE(fine, 4);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's B slice has landed
+            SPMM_FINE(fine, 5);
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0)
-                ptx::mbar_arrive(tile_full(w));
+                ptx::mbar_arrive(tile_full(s_own));
+            SPMM_FINE(fine, 6);
+            j = j_next;
         }
         ptx::cp_async_wait_all();
+        if (s_own == 0 && h == 0)
+            SPMM_TRACE(6);
     }
-    else if (warp == kMmaWarp) {
+    else if (warp >= kFirstMmaWarp) {
         // ------------------------------------------------------------ MMA issue
+        // Lane 0 of MMA warp q issues the MMAs of tiles q, q + Q, ... (chunk-local numbering) into
+        // accumulator (q, segment parity); a segment is the run of tiles that share a row of tiles.
+        // Every MMA warp arrives on the segment's acc_full barrier, through tcgen05.commit if it
+        // issued anything for the segment and directly otherwise.
+        const int q = warp - kFirstMmaWarp;
         if (lane == 0) {
-            constexpr uint32_t idesc = ptx::make_idesc_f16_f32(kTileRows, NB, false, true);
-            int                seg   = 0;
+            constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(kTileRows, NB, false, true);
+            const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
+            const uint64_t     b_desc0 = ptx::make_smem_desc(b_base, BT::kGroupBytes, BT::kGroupBytes, BT::kSwizzleMode);
+            bool ok  = true;
+            int  seg = 0;
 #pragma unroll 1
-            for (int l = 0; l < num_tiles; l++) {
-                const int  j     = (tile_begin + l) % tiles_k;
-                const int  s     = l % D;
-                const bool first = (l == 0) || (j == 0);
-                if (first && seg >= 2 && !ptx::mbar_wait_bounded(acc_free(seg & 1), ((seg >> 1) - 1) & 1, abort_word))
-                    break;
-                if (!ptx::mbar_wait_bounded(tile_full(s), (l / D) & 1, abort_word))
-                    break;
-                ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + (seg & 1) * NB;
-                const uint64_t a_desc = ptx::make_smem_desc(a_base + s * kATileBytes, 16, 1024, ptx::kSwizzle128B);
-                const uint64_t b_desc =
-                    ptx::make_smem_desc(b_base + s * BT::kBytes, BT::kGroupBytes, BT::kGroupBytes, BT::kSwizzleMode);
+            for (int l0 = 0; l0 < num_tiles && ok; ++seg) {
+                const int j0    = (tile_begin + l0) % tiles_k;
+                const int len   = min(tiles_k - j0, num_tiles - l0);
+                const int first = l0 + ((q - l0) % Q + Q) % Q;
+                const uint32_t d_tmem = tmem_base + ((seg & 1) * Q + q) * NB;
+                if (seg >= 2)
+                    ok = ptx::mbar_wait_bounded(acc_free(seg & 1), ((seg >> 1) - 1) & 1, abort_word);
+                uint32_t accumulate = 0;
+#pragma unroll 1
+                for (int l = first; l < l0 + len && ok; l += Q) {
+                    const int      s      = l % D;
+                    const uint32_t parity = (l / D) & 1;
+                    ok = ptx::mbar_wait_bounded(tile_full(s), parity, abort_word);
+                    if (!ok)
+                        break;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kATileBytes >> 4));
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((parity * D + s) * (BT::kBytes >> 4));
 #pragma unroll
-                for (int k = 0; k < kTileCols / 16; k++) {
-                    // A: 16 k values = 32 bytes along the swizzled row; B: 16 k rows = two 8-row groups.
-                    ptx::umma_f16_ss(d_tmem,
-                                     a_desc + static_cast<uint64_t>((k * 32) >> 4),
-                                     b_desc + static_cast<uint64_t>((k * 2 * BT::kGroupBytes) >> 4),
-                                     idesc,
-                                     (first && k == 0) ? 0u : 1u);
+                    for (int k = 0; k < ((ABL & 8) ? 0 : kTileCols / 16); k++) {
+                        // A: 16 k values = 32 bytes along the swizzled row; B: 16 k rows = two 8-row groups.
+                        ptx::umma_f16_ss(d_tmem,
+                                         a_desc + static_cast<uint64_t>((k * 32) >> 4),
+                                         b_desc + static_cast<uint64_t>((k * 2 * BT::kGroupBytes) >> 4),
+                                         idesc,
+                                         k == 0 ? accumulate : 1u);
+                    }
+                    ptx::umma_commit(tile_free(s));
+                    accumulate = 1;
                 }
-                ptx::umma_commit(tile_free(s));
-                if (j == tiles_k - 1 || l == num_tiles - 1) {
-                    ptx::umma_commit(acc_full(seg & 1));
-                    seg++;
+                if (ok) {
+                    if (first < l0 + len)
+                        ptx::umma_commit(acc_full(seg & 1));
+                    else
+                        ptx::mbar_arrive(acc_full(seg & 1));
                 }
+                l0 += len;
             }
         }
     }
@@ -257,18 +394,32 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const int  j0       = t0 % tiles_k;
             const int  len      = min(tiles_k - j0, num_tiles - l);
             const bool whole    = (j0 == 0) && (len == tiles_k);
-            if (!ptx::mbar_wait_bounded(acc_full(seg & 1), (seg >> 1) & 1, abort_word))
+            if (!warp_wait(acc_full(seg & 1), (seg >> 1) & 1, abort_word, lane))
                 break;
             ptx::tc_fence_after_sync();
-            float          acc[N];
-            const uint32_t taddr = tmem_base + (seg & 1) * NB + (static_cast<uint32_t>(warp * 32) << 16);
-            if (N == 8) {
-                ptx::tmem_ld_x8(taddr, reinterpret_cast<uint32_t*>(acc));
-            }
-            else {
+            // Add the accumulators of the MMA warps that issued for this segment, in warp order.
+            float acc[N];
 #pragma unroll
-                for (int c = 0; c < N / 16; c++)
-                    ptx::tmem_ld_x16(taddr + c * 16, reinterpret_cast<uint32_t*>(acc) + c * 16);
+            for (int n = 0; n < N; n++)
+                acc[n] = 0.0f;
+#pragma unroll
+            for (int q = 0; q < Q; q++) {
+                if (((q - l) % Q + Q) % Q < len) {
+                    float          part[N];
+                    const uint32_t taddr = tmem_base + ((seg & 1) * Q + q) * NB + (static_cast<uint32_t>(warp * 32) << 16);
+                    if (N == 8) {
+                        ptx::tmem_ld_x8(taddr, reinterpret_cast<uint32_t*>(part));
+                    }
+                    else {
+#pragma unroll
+                        for (int c = 0; c < N / 16; c++)
+                            ptx::tmem_ld_x16(taddr + c * 16, reinterpret_cast<uint32_t*>(part) + c * 16);
+                    }
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int n = 0; n < N; n++)
+                        acc[n] += part[n];
+                }
             }
             ptx::tmem_ld_wait();
             ptx::tc_fence_before_sync();
@@ -353,11 +504,14 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     }
 
     // ---------------------------------------------------------------- exit
+    if (warp == kFirstMmaWarp) SPMM_TRACE(7);   // MMA lane done issuing
+    if (warp == 0) SPMM_TRACE(8);          // epilogue warp 0 done
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if (warp == 0) SPMM_TRACE(9);
     if (threadIdx.x == 0 && *abort_word != 0)
         atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
-    if (warp == kMmaWarp) {
+    if (warp == kFirstMmaWarp) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
