@@ -1,0 +1,367 @@
+"""Benchmark of the sparse-weight SpMM hot path on B200.
+
+A step is one pass over the four linear layers of an OPT-66B decoder block at decode size
+(QKV 27648x9216, out-proj 9216x9216, FFN1 36864x9216, FFN2 9216x36864; N = 16 tokens, 80 %
+i.i.d. sparsity, fp16 in, fp32 accumulate): four SpMM launches through the C boundary of
+libSpMM_API.so.  Weights are seeded synthetic stand-ins for pruned OPT weights, encoded with
+the library's InitSparseMatrixA_API and resident in HBM before the timed region.
+
+    python bench.py --gpus N --steps K --warmup W [--impl reference]
+
+Prints one JSON line (rank 0).  `value` is effective weight-HBM GB/s, (4*NNZ_pad +
+4*NumOffsets) summed over the step and all ranks, divided by the device time (max over
+ranks).  With N > 1 every rank runs the same per-GPU workload on its own row shard of an
+N-times taller, column-parallel layer: no collective on the data path, weak scaling.
+"""
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+import numpy as np
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+LAYERS = [  # name, M, K, Split_K (sizes the workspace: Split_K * M * N * 2 bytes)
+    ("qkv", 27648, 9216, 4),
+    ("out_proj", 9216, 9216, 8),
+    ("ffn1", 36864, 9216, 4),
+    ("ffn2", 9216, 36864, 8),
+]
+N_TOKENS = 16
+SPARSITY = 0.8
+WORKLOAD = "opt66b_decoder_block_4_spmm_n16_p0.8"
+HBM_PEAK_FALLBACK_GBS = 6650.0
+
+
+def measured_hbm_peak():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return HBM_PEAK_FALLBACK_GBS, "fallback"
+
+
+class ClockSampler(threading.Thread):
+    """Samples SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.reasons, self.max_mhz = index, [], set(), None
+        self._stop_flag = threading.Event()
+        self.window = None
+
+    def run(self):
+        try:
+            import pynvml
+            pynvml.nvmlInit()
+            h = pynvml.nvmlDeviceGetHandleByIndex(self.index)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM)
+            names = {
+                "hw_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonHwSlowdown", 0x8),
+                "hw_thermal_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonHwThermalSlowdown", 0x40),
+                "sw_thermal_slowdown": getattr(pynvml, "nvmlClocksThrottleReasonSwThermalSlowdown", 0x20),
+                "sw_power_cap": getattr(pynvml, "nvmlClocksThrottleReasonSwPowerCap", 0x4),
+            }
+            while not self._stop_flag.is_set():
+                mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
+                mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                self.samples.append((time.time(), mhz))
+                if self.window and self.window[0] <= time.time():
+                    for name, bit in names.items():
+                        if mask & bit:
+                            self.reasons.add(name)
+                time.sleep(0.005)
+        except Exception as e:  # NVML missing: report that instead of clocks
+            self.reasons.add("nvml_unavailable:%s" % type(e).__name__)
+
+    def stop(self):
+        self._stop_flag.set()
+        self.join(timeout=2)
+
+    def summary(self, t0, t1):
+        inside = [m for (t, m) in self.samples if t0 <= t <= t1] or [m for (_, m) in self.samples[-3:]]
+        return {"sm_mhz": float(np.median(inside)) if inside else None, "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(inside)}
+
+
+def algorithmic_bytes(n_words, n_offsets, M, K, N):
+    """Compulsory traffic of one SpMM: words + offsets + B + C."""
+    return 4 * n_words + 4 * n_offsets + 2 * K * N + 2 * M * N
+
+
+def make_layer(sp, name, M, K, seed):
+    A = sp.synth_fp16((M, K), seed, 0.02, SPARSITY)
+    words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, N_TOKENS, K)
+    del A
+    return words, offsets, n_offsets
+
+
+def run_ours(args):
+    import torch
+    import torch.distributed as dist
+
+    import graphneuralnetproj_b200 as sp
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+
+    # ---- weights: encoded on the host, resident in HBM (rank r holds row shard r of each layer)
+    layers = []
+    weight_bytes = algo_bytes = 0
+    for li, (name, M, K, sk) in enumerate(LAYERS):
+        words, offsets, n_offsets = make_layer(sp, name, M, K, 0xA000 + 16 * rank + li)
+        weight_bytes += 4 * words.size + 4 * n_offsets
+        algo_bytes += algorithmic_bytes(words.size, n_offsets, M, K, N_TOKENS)
+        B_host = torch.from_numpy(sp.synth_fp16((K, N_TOKENS), 0xB000 + li, 1.0).view(np.int16)).pin_memory()
+        layers.append(dict(
+            name=name, M=M, K=K, sk=sk,
+            words=torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev),
+            offsets=torch.from_numpy(offsets).to(dev),
+            B_host=B_host, B=B_host.to(dev),
+            C=torch.zeros((M, N_TOKENS), dtype=torch.int16, device=dev),
+            C_host=torch.zeros((M, N_TOKENS), dtype=torch.int16).pin_memory(),
+            ws=torch.zeros(sp.workspace_bytes(M, N_TOKENS, sk) // 2, dtype=torch.int16, device=dev)))
+        del words
+
+    def launch(layer):
+        rc = sp.SpMM_SplitK_API(None, None, layer["words"], None, None, layer["offsets"], layer["B"], layer["C"],
+                                layer["M"], N_TOKENS, layer["K"], layer["ws"], layer["sk"])
+        if rc != 0:
+            raise RuntimeError("SpMM_SplitK_API failed with cudaError %d" % rc)
+
+    def step():
+        for layer in layers:
+            launch(layer)
+
+    def step_e2e():
+        for layer in layers:
+            layer["B"].copy_(layer["B_host"], non_blocking=True)
+            launch(layer)
+            layer["C_host"].copy_(layer["C"], non_blocking=True)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        for _ in range(max(args.warmup, 3)):
+            step()
+        torch.cuda.synchronize()
+        # One step captured as a CUDA graph so that launch latency of the host loop is not timed.
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            step()
+        graph.replay()
+        sampler = ClockSampler(local)
+        sampler.start()
+        barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.time()
+        sampler.window = (t0, None)
+        e0.record(stream)
+        for _ in range(args.steps):
+            graph.replay()
+        e1.record(stream)
+        barrier()
+        t1 = time.time()
+        sampler.stop()
+        ms = e0.elapsed_time(e1)
+
+        # per-layer device time: events around every launch of a few plain (un-captured) steps, so
+        # each layer's weights have been evicted from L2 by the other layers in between
+        reps, pairs = 10, []
+        for _ in range(reps):
+            for layer in layers:
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                launch(layer)
+                b.record(stream)
+                pairs.append((layer["name"], a, b))
+        torch.cuda.synchronize()
+        per_layer = {}
+        for name, a, b in pairs:
+            per_layer[name] = per_layer.get(name, 0.0) + a.elapsed_time(b) * 1000.0 / reps
+
+        # end to end: activations from pinned host memory, results back to the host, every launch
+        for _ in range(3):
+            step_e2e()
+        barrier()
+        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        f0.record(stream)
+        for _ in range(args.steps):
+            step_e2e()
+        f1.record(stream)
+        barrier()
+        ms_e2e = f0.elapsed_time(f1)
+    status = sp.device_status()
+    if status != 0:
+        raise RuntimeError("device status %d: a bounded wait inside the kernel gave up" % status)
+
+    times = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(times, op=dist.ReduceOp.MAX)
+    ms, ms_e2e = times.tolist()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+    ms_per_step = ms / args.steps
+    value = world * weight_bytes / (ms_per_step * 1e-3) / 1e9
+    e2e_value = world * weight_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
+    peak, peak_kind = measured_hbm_peak()
+    achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9  # this rank's kernel launches
+    line = {
+        "metric": "effective weight-HBM GB/s, SpMM (OPT-66B shapes, N=16, 80% sparse)",
+        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "layers": [[n, m, k] for n, m, k, _ in LAYERS], "n_tokens": N_TOKENS,
+                   "sparsity": SPARSITY, "split_k": [s for *_, s in LAYERS], "parallelism": "column-parallel by M x%d" % world,
+                   "l2_policy": "inputs larger than L2: %.0f MB of weights per step" % (weight_bytes / 1e6),
+                   "spmm_us_per_layer": {k: round(v, 2) for k, v in per_layer.items()},
+                   "weight_bytes_per_step_per_gpu": weight_bytes},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
+                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
+                     "kernel": "spmm_decode_kernel<16>", "algorithmic_bytes_per_step": algo_bytes},
+        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
+                "h2d_bytes_per_step": sum(2 * L["K"] * N_TOKENS for L in layers),
+                "d2h_bytes_per_step": sum(2 * L["M"] * N_TOKENS for L in layers)},
+        "gpu_launches": args.steps * len(layers),
+        "clocks": sampler.summary(t0, t1),
+    }
+    if world == 1 and not args.no_cpu_baseline:
+        line["cpu_baseline"] = cpu_baseline()
+    print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+def cpu_sample_problem(sp, rows, K, seed):
+    A = sp.synth_fp16((rows, K), seed, 0.02, SPARSITY)
+    B = sp.synth_fp16((K, N_TOKENS), seed + 1, 1.0)
+    return A, B
+
+
+def cpu_spmm_threads(oracle, words, offsets, B, M, K, threads):
+    """The oracle's decode + fp32-accumulate product over row blocks of tiles, one block per host thread."""
+    tiles_m, tiles_k = M // 128, K // 64
+    threads = max(1, min(threads, tiles_m))
+    out = [None] * threads
+
+    def work(t):
+        r0, r1 = tiles_m * t // threads, tiles_m * (t + 1) // threads
+        offs = offsets[r0 * tiles_k:r1 * tiles_k + 1].astype(np.int64)
+        sub_offsets = np.concatenate([offs - offs[0], [offs[-1] - offs[0]]]).astype(np.int32)
+        sub_words = words[offs[0] * 4:offs[-1] * 4]
+        out[t] = oracle.spmm_from_csl(sub_words, sub_offsets, B, (r1 - r0) * 128, K)
+
+    pool = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+    for th in pool:
+        th.start()
+    for th in pool:
+        th.join()
+    return np.concatenate(out, axis=0)
+
+
+def cpu_baseline():
+    """Reference CPU path on a bounded sample: the reference's own InitSparseMatrixA_API (one
+    core; it is single-threaded) and the oracle's decode + fp32 host product (one core)."""
+    import graphneuralnetproj_b200 as sp
+    import oracle
+    M, K = 9216, 9216  # the out-proj layer of the step
+    A, B = cpu_sample_problem(sp, M, K, 0xC000)
+    t0 = time.time()
+    if oracle.have_ref():
+        words, offsets = oracle.ref_encode(A)
+        encoder = "reference InitSparseMatrixA_API (oracle/_ref)"
+    else:
+        words, offsets = oracle.encode(A)
+        encoder = "oracle port of InitSparseMatrixA_API"
+    t_enc = time.time() - t0
+    t0 = time.time()
+    oracle.spmm_from_csl(words, offsets, B, M, K)
+    t_spmm = time.time() - t0
+    wbytes = 4 * words.size + 4 * offsets.size
+    return {"value": round(wbytes / t_spmm / 1e9, 4), "unit": "GB/s", "cores": 1, "kind": "port",
+            "sample": "out-proj layer 9216x9216, N=16, p=0.8: %s %.2f s on 1 core; oracle decode + fp32 host "
+                      "product %.2f s on 1 core (value = weight bytes / product time)" % (encoder, t_enc, t_spmm),
+            "encode_s": round(t_enc, 3), "spmm_s": round(t_spmm, 3)}
+
+
+def run_reference(args):
+    """The reference's CPU implementation of the path on all host cores: decode of the tiled-CSL
+    words + fp32-accumulate host product, a bounded row sample of the out-proj layer per step."""
+    if int(os.environ.get("RANK", "0")) != 0:
+        return
+    import graphneuralnetproj_b200 as sp
+    import oracle
+    cores = os.cpu_count() or 1
+    K = 9216
+    rows = 9216
+    A, B = cpu_sample_problem(sp, rows, K, 0xC000)
+    words, offsets = (oracle.ref_encode(A) if oracle.have_ref() else oracle.encode(A))
+    t0 = time.time()
+    cpu_spmm_threads(oracle, words, offsets, B, rows, K, cores)
+    probe = time.time() - t0
+    # bound the whole run to about two minutes
+    budget = 120.0 / max(args.steps + args.warmup, 1)
+    if probe > budget:
+        rows = max(128, int(rows * budget / probe) // 128 * 128)
+        tiles_k = K // 64
+        offs = offsets[:rows // 128 * tiles_k + 1]
+        offsets = np.concatenate([offs, offs[-1:]]).astype(np.int32)
+        words = words[:int(offs[-1]) * 4]
+    for _ in range(args.warmup):
+        cpu_spmm_threads(oracle, words, offsets, B, rows, K, cores)
+    t0 = time.time()
+    for _ in range(args.steps):
+        cpu_spmm_threads(oracle, words, offsets, B, rows, K, cores)
+    dt = (time.time() - t0) / args.steps
+    wbytes = 4 * words.size + 4 * offsets.size
+    value = round(wbytes / dt / 1e9, 4)
+    sample = "%d x %d rows of the out-proj layer per step, N=16, p=0.8, %d host threads" % (rows, K, cores)
+    line = {
+        "impl": "reference", "metric": "effective weight-HBM GB/s, SpMM (OPT-66B shapes, N=16, 80% sparse)",
+        "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "f16", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "sample": sample},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores,
+                         "kind": "port", "sample": sample + "; encoder: " +
+                         ("reference (oracle/_ref)" if oracle.have_ref() else "oracle port")},
+        "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()
