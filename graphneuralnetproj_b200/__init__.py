@@ -11,6 +11,7 @@ from .spmm_api import (  # noqa: F401
     decompose,
     device_status,
     plan,
+    spmm_own_scratch,
     synth_fp16,
     workspace_bytes,
 )

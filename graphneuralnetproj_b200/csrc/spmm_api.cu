@@ -202,6 +202,106 @@ cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
     }
 }
 
+// ------------------------------------------------------------------ entry point that allocates nothing
+namespace spmm_b200 {
+namespace {
+
+// Scratch for the fp32 partial tiles of split rows, for callers that cannot provide a workspace.
+// It lives in the library image: every GPU that loads the library holds these 10 MiB until the
+// process exits.  In host code the name below is only a handle; the device address comes from
+// cudaGetSymbolAddress.
+constexpr size_t kOwnScratchBytes = 10u << 20;
+static __device__ __align__(256) float g_own_scratch[kOwnScratchBytes / sizeof(float)];
+
+// Device address of g_own_scratch on `device` (which must be current), looked up once per device.
+cudaError_t own_scratch_address(int device, float** out)
+{
+    static float*     address[64] = {};
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    float*& slot = address[device & 63];
+    if (slot == nullptr) {
+        void*       p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_own_scratch);
+        if (e != cudaSuccess)
+            return e;
+        slot = static_cast<float*>(p);
+    }
+    *out = slot;
+    return cudaSuccess;
+}
+
+}  // namespace
+}  // namespace spmm_b200
+
+extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
+                                          const void* Compressed_A,
+                                          const int*  TileOffsets,
+                                          const void* B,
+                                          void*       C,
+                                          int         M_Global,
+                                          int         N_Global,
+                                          int         K_Global)
+{
+    using namespace spmm_b200;
+    if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
+        printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
+        return static_cast<int>(cudaErrorUnknown);
+    }
+    if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kTileCols != 0) {
+        printf("spmm_b200_spmm_own_scratch: M (%d) must be a positive multiple of %d and K (%d) of %d\n", M_Global,
+               kTileRows, K_Global, kTileCols);
+        return static_cast<int>(cudaErrorInvalidValue);
+    }
+    if (M_Global / kTileRows > kMaxRowTiles) {
+        printf("spmm_b200_spmm_own_scratch: M = %d exceeds the supported maximum of %d rows\n", M_Global,
+               kMaxRowTiles * kTileRows);
+        return static_cast<int>(cudaErrorInvalidValue);
+    }
+    if (!Compressed_A || !TileOffsets || !B || !C || !aligned16(Compressed_A) || !aligned16(B) || !aligned16(C))
+        return static_cast<int>(cudaErrorInvalidValue);
+    int         device = 0;
+    cudaError_t e      = cudaGetDevice(&device);
+    if (e != cudaSuccess)
+        return static_cast<int>(e);
+    DeviceInfo& dev = device_info(device);
+    const int   tiles_m = M_Global / kTileRows, tiles_k = K_Global / kTileCols;
+    const long  total   = static_cast<long>(tiles_m) * tiles_k;
+    const size_t slot_bytes = static_cast<size_t>(kTileRows) * N_Global * sizeof(float);
+    // The balanced partition over all SMs must fit: its partial tiles are what the scratch is for.
+    Schedule full;
+    fill_schedule(full, tiles_m, tiles_k, static_cast<int>(total < dev.sm_count ? total : dev.sm_count), 1);
+    if (static_cast<size_t>(full.slots_used) * slot_bytes > kOwnScratchBytes) {
+        printf("spmm_b200_spmm_own_scratch: this shape needs %zu bytes of scratch, the built-in array holds %zu\n",
+               static_cast<size_t>(full.slots_used) * slot_bytes, kOwnScratchBytes);
+        return static_cast<int>(cudaErrorInvalidValue);
+    }
+    float* scratch = nullptr;
+    e              = own_scratch_address(device, &scratch);
+    if (e != cudaSuccess)
+        return static_cast<int>(e);
+    DecodeParams params;
+    params.words        = static_cast<const uint4*>(Compressed_A);
+    params.tile_offsets = TileOffsets;
+    params.B            = static_cast<const half*>(B);
+    params.C            = static_cast<half*>(C);
+    params.slots        = scratch;
+    params.n            = N_Global;
+    params.tiles_k      = tiles_k;
+    params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, static_cast<long>(kOwnScratchBytes / slot_bytes)});
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    switch (N_Global) {
+        case 8:
+            return static_cast<int>(launch_decode<8>(st, dev, 0, params));
+        case 16:
+            return static_cast<int>(launch_decode<16>(st, dev, 1, params));
+        case 32:
+            return static_cast<int>(launch_decode<32>(st, dev, 2, params));
+        default:
+            return static_cast<int>(launch_decode<64>(st, dev, 3, params));
+    }
+}
+
 // ------------------------------------------------------------------ extern "C"
 extern "C" {
 #ifdef SPMM_B200_ABLATIONS

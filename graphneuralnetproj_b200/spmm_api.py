@@ -41,6 +41,8 @@ def _load():
     lib.spmm_b200_spmm_splitk.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_void_p] + [ctypes.c_void_p] * 2 + \
         [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
     lib.spmm_b200_spmm_splitk.restype = ctypes.c_int
+    lib.spmm_b200_spmm_own_scratch.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3
+    lib.spmm_b200_spmm_own_scratch.restype = ctypes.c_int
     lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
     for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):
@@ -126,6 +128,18 @@ def SpMM_SplitK_API(stream, A, Compressed_A, A1_Ind_data, metadata, TileOffsets,
     return LIB.spmm_b200_spmm_splitk(ctypes.c_void_p(handle), _dev_ptr(A), _dev_ptr(Compressed_A), _dev_ptr(A1_Ind_data),
                                      _dev_ptr(metadata), _dev_ptr(TileOffsets), _dev_ptr(B), _dev_ptr(C), M_Global,
                                      N_Global, K_Global, _dev_ptr(Reduction_Workspace), Split_K)
+
+
+def spmm_own_scratch(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global):
+    """SpMM for callers that cannot allocate or pass a workspace: partial tiles go to a 10 MiB array
+    built into the library.  Same result as SpMM_SplitK_API; returns the cudaError_t as an int.
+    Make the first call on a device before any stream capture begins; calls on one device must not overlap."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    handle = stream if isinstance(stream, int) else stream.cuda_stream
+    return LIB.spmm_b200_spmm_own_scratch(ctypes.c_void_p(handle), _dev_ptr(Compressed_A), _dev_ptr(TileOffsets),
+                                          _dev_ptr(B), _dev_ptr(C), M_Global, N_Global, K_Global)
 
 
 def workspace_bytes(M_Global, N_Global, Split_K):

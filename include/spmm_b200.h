@@ -49,6 +49,31 @@ int spmm_b200_spmm_splitk(void*       stream,
                           void*       Reduction_Workspace,
                           int         Split_K);
 
+/* SpMM for callers that can neither allocate device memory nor bring a workspace: a plugin or
+ * serving callback that is handed only the tensors of the call, a host that has frozen its
+ * allocator after start-up, a latency-critical loop in which cudaMalloc's implicit
+ * synchronisation is not acceptable.  It has no counterpart in the reference, whose
+ * SpMM_SplitK_API always needs a caller-allocated Reduction_Workspace.  Same result as
+ * spmm_b200_spmm_splitk in unstructured mode; the fp32 partial tiles of rows shared between
+ * thread blocks go to a 10 MiB array built into the library instead (each GPU that loads the
+ * library holds it until the process exits).  Nothing is allocated or freed here, by the CUDA
+ * runtime or any other library.  Limits: N in {8, 16, 32, 64}; M a multiple of 128 up to
+ * 1,048,576; K a multiple of 64; and the partition's partial tiles must fit the 10 MiB -- a
+ * shape beyond that is refused with a message and cudaErrorInvalidValue.  The first call on each
+ * device looks up the array's device address (the device must be current); that first call
+ * should come before any stream capture begins.  All calls on a device share the array and it keeps the previous
+ * call's partial tiles (each slot is rewritten before it is read, so nothing needs clearing);
+ * calls that overlap in time on one device race on it, and with every other SpMM of this
+ * library through the shared arrival counters. */
+int spmm_b200_spmm_own_scratch(void*       stream,
+                               const void* Compressed_A,
+                               const int*  TileOffsets,
+                               const void* B,
+                               void*       C,
+                               int         M_Global,
+                               int         N_Global,
+                               int         K_Global);
+
 /* The reference's workspace contract, build/SpMM_API.cuh:34-38:
  * Split_K * M * N * sizeof(half) bytes. */
 size_t spmm_b200_workspace_bytes(int M_Global, int N_Global, int Split_K);
