@@ -81,8 +81,14 @@ constexpr uint32_t kSuspendNs   = 20000u;
 
 __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word)
 {
-    if (mbar_try_wait(bar, parity))
-        return true;
+#ifndef SPMM_B200_PLAIN_POLLS
+#define SPMM_B200_PLAIN_POLLS 64
+#endif
+    // plain polls first: a parked thread wakes up noticeably later than a polling one
+#pragma unroll 1
+    for (int i = 0; i < SPMM_B200_PLAIN_POLLS; i++)
+        if (mbar_try_wait(bar, parity))
+            return true;
     uint64_t start = 0;
 #pragma unroll 1
     for (uint32_t polls = 0;; polls++) {
@@ -123,6 +129,12 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src
                  "r"(bytes),
                  "r"(bar)
                  : "memory");
+}
+
+// Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2.
+__device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes)
+{
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
 // Streaming 128-bit load of read-only data that is used exactly once.

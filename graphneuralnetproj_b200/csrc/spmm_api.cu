@@ -72,7 +72,12 @@ template<int D, int Q, int WPT, int ABL>
 cudaError_t launch_ablated(cudaStream_t stream, const DecodeParams& params)
 {
     constexpr int smem = decode_smem_bytes<16, D>();
-    auto kern = spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL>;
+    const char* envt = getenv("SPMM_B200_TURNS");
+    const int turns = envt ? atoi(envt) : 0;
+    auto kern = turns == 1 ? spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, 1>
+              : turns == 2 ? spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, (D % 2 == 0 ? 2 : 0)>
+              : turns == 4 ? spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, (D > 4 && D % 4 == 0 ? 4 : 0)>
+                           : spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, 0>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     kern<<<params.sched.num_ctas, decode_threads<D, Q, WPT>(), smem, stream>>>(params);
     return cudaGetLastError();
@@ -86,6 +91,12 @@ cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, in
         case 3: return launch_ablated<D, Q, WPT, 3>(stream, params);
         case 4: return launch_ablated<D, Q, WPT, 4>(stream, params);
         case 12: return launch_ablated<D, Q, WPT, 12>(stream, params);
+        case 13: return launch_ablated<D, Q, WPT, 13>(stream, params);
+        case 28: return launch_ablated<D, Q, WPT, 28>(stream, params);
+        case 29: return launch_ablated<D, Q, WPT, 29>(stream, params);
+        case 30: return launch_ablated<D, Q, WPT, 30>(stream, params);
+        case 14: return launch_ablated<D, Q, WPT, 14>(stream, params);
+        case 15: return launch_ablated<D, Q, WPT, 15>(stream, params);
         case 9: return launch_ablated<D, Q, WPT, 9>(stream, params);
         case 10: return launch_ablated<D, Q, WPT, 10>(stream, params);
         case 8: return launch_ablated<D, Q, WPT, 8>(stream, params);
@@ -106,6 +117,9 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
         const int abl = env ? atoi(env) : 0;
         switch (envd ? atoi(envd) : 842) {   // D * 100 + Q * 10 + WPT
             case 841: return launch_ablated_d<8, 4, 1>(stream, params, abl);
+            case 441: return launch_ablated_d<4, 4, 1>(stream, params, abl);
+            case 1021: return launch_ablated_d<10, 2, 1>(stream, params, abl);
+            case 821: return launch_ablated_d<8, 2, 1>(stream, params, abl);
             case 822: return launch_ablated_d<8, 2, 2>(stream, params, abl);
             case 1022: return launch_ablated_d<10, 2, 2>(stream, params, abl);
             case 1052: return launch_ablated_d<10, 5, 2>(stream, params, abl);

@@ -109,7 +109,7 @@ struct BTile {
 template<int NB, int D>
 constexpr int decode_smem_bytes()
 {
-    return 1024 + D * (kATileBytes + 2 * BTile<NB>::kBytes) + 256;  // per ring slot: one A buffer, two B buffers
+    return 1024 + D * (kATileBytes + 2 * BTile<NB>::kBytes) + 512;  // per ring slot: one A buffer, two B buffers
 }
 
 template<int D, int Q, int WPT>
@@ -141,7 +141,11 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // VPL : 4-word vectors held per lane
 // ABL : debugging ablation mask (0 in production): 1 no clearing, 2 no scatter, 4 no word loads,
 //       8 no MMA, 16 no B copy
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0>
+// TURNS : at most this many ring slots are cleared and scattered at the same time (0 = no limit).
+//         Decoders that share the load/store unit evenly all finish together and then all wait for
+//         their MMAs together, so the store phase and the MMA round trip add up instead of
+//         overlapping; taking turns keeps the hand-overs staggered.
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TURNS = 0>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
@@ -157,7 +161,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     auto tile_free = [&](int s) { return bar_base + 8u * (D + s); };
     auto acc_full  = [&](int b) { return bar_base + 8u * (2 * D + b); };
     auto acc_free  = [&](int b) { return bar_base + 8u * (2 * D + 2 + b); };
-    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * D + 4);
+    auto turn = [&](int s) { return bar_base + 8u * (2 * D + 4 + s); };
+    const uint32_t tmem_slot_addr = bar_base + 8u * (3 * D + 4);
     uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
     volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
@@ -173,6 +178,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     constexpr int      kFirstDecodeWarp = kFirstMmaWarp + Q;
     constexpr uint32_t kTmemCols        = tmem_columns(2 * Q * NB);  // accumulator (q, b) at column (b * Q + q) * NB
     static_assert(2 * Q * NB <= 512, "accumulators exceed the 512 TMEM columns");
+    static_assert(D % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
+    static_assert(TURNS < D && (TURNS == 0 || D % TURNS == 0),
+                  "TURNS must divide D: the next arrival on a turn barrier must depend on its current waiter");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < D; s++) {
@@ -182,6 +190,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         for (int b = 0; b < 2; b++) {
             ptx::mbar_init(acc_full(b), Q);
             ptx::mbar_init(acc_free(b), kEpilogueWarps);
+        }
+        for (int s = 0; s < D; s++) {
+            ptx::mbar_init(turn(s), WPT);
         }
         *abort_word = 0;
         ptx::mbar_init_fence();
@@ -252,6 +263,14 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 }
         };
         const uint4* src = p.words + lane_vec;  // always offset by this lane's first vector
+        // Offsets are read two tiles ahead (next*: tile l + D, after*: tile l + 2D) so that the words of
+        // tile l + 2D can be requested into L2 while tile l is being decoded; the register loads of
+        // tile l + D, issued after this tile's scatter, then find their lines in L2.
+        int  after0 = 0, after1 = 0;
+        auto prefetch_tile = [&](int off0, int off1) {
+            if (h == 0 && lane == 0 && off1 > off0)
+                ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
+        };
         if (s_own < num_tiles) {
             const int off0 = __ldg(p.tile_offsets + tile_begin + s_own);
             const int off1 = __ldg(p.tile_offsets + tile_begin + s_own + 1);
@@ -262,6 +281,12 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             if (s_own + D < num_tiles) {
                 next0 = __ldg(p.tile_offsets + tile_begin + s_own + D);
                 next1 = __ldg(p.tile_offsets + tile_begin + s_own + D + 1);
+                prefetch_tile(next0, next1);
+            }
+            if (s_own + 2 * D < num_tiles) {
+                after0 = __ldg(p.tile_offsets + tile_begin + s_own + 2 * D);
+                after1 = __ldg(p.tile_offsets + tile_begin + s_own + 2 * D + 1);
+                prefetch_tile(after0, after1);
             }
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
@@ -273,6 +298,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const bool has_next = l + D < num_tiles;
             const bool fine     = (s_own == 0 && h == 0 && use == 8);
             SPMM_FINE(fine, 0);
+            if (use > 0 && l + 2 * D < num_tiles)
+                prefetch_tile(after0, after1);  // offsets were requested one iteration ago
             if (use > 0) {
                 if (!ptx::mbar_wait_bounded(tile_free(s_own), (use - 1) & 1, abort_word)) {
                     // A team mate that saw the barrier complete may be waiting at the team barrier below.
@@ -281,6 +308,18 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     break;
                 }
                 SPMM_FINE(fine, 7);
+            }
+            if (TURNS > 0 && l >= TURNS) {
+                // wait until tile l - TURNS has been scattered: the decoder of slot (l - TURNS) % D arrives
+                // on this slot's turn barrier; slots below TURNS get no arrival for their first tile
+                const uint32_t phase = s_own < TURNS ? (use - 1) : use;
+                if (!ptx::mbar_wait_bounded(turn(s_own), phase & 1, abort_word)) {
+                    if (WPT > 1)
+                        asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
+                    break;
+                }
+            }
+            if (use > 0) {
                 if (!(ABL & 1))
                     zero_a();
                 team_sync();  // the whole buffer is clear before anyone scatters into it
@@ -305,14 +344,21 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 for (int idx = lane_vec + VPL * WPT * 32; idx < nvec; idx += WPT * 32)
                     ptx::scatter_words(a_tile, ptx::ld_stream_128(src - lane_vec + idx));
             }
+            if (TURNS > 0) {
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive(turn((s_own + TURNS) % D));  // tile l + TURNS may start its stores
+            }
             SPMM_FINE(fine, 3);
             if (has_next) {
                 nvec = next1 - next0;
                 src  = p.words + next0 + lane_vec;
                 load_words(src, nvec);
-                if (l + 2 * D < num_tiles) {
-                    next0 = __ldg(p.tile_offsets + tile_begin + l + 2 * D);
-                    next1 = __ldg(p.tile_offsets + tile_begin + l + 2 * D + 1);
+                next0 = after0;
+                next1 = after1;
+                if (l + 3 * D < num_tiles) {
+                    after0 = __ldg(p.tile_offsets + tile_begin + l + 3 * D);
+                    after1 = __ldg(p.tile_offsets + tile_begin + l + 3 * D + 1);
                 }
             }
             SPMM_FINE(fine, 4);
