@@ -36,6 +36,9 @@ N_TOKENS = 16
 SPARSITY = 0.8
 WORKLOAD = "opt66b_decoder_block_4_spmm_n16_p0.8"
 HBM_PEAK_FALLBACK_GBS = 6650.0
+# dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture summarised in
+# profiles/spmm_decode_n16_ffn1_outproj_full_capture.md (FFN1 launch: 277.16 MB / 273.0 MB)
+DRAM_TRAFFIC_OVER_ALGORITHMIC = 1.015
 
 
 def measured_hbm_peak():
@@ -236,7 +239,10 @@ def run_ours(args):
                    "spmm_us_per_layer": {k: round(v, 2) for k, v in per_layer.items()},
                    "weight_bytes_per_step_per_gpu": weight_bytes},
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4), "traffic": None, "peak_source": peak_kind,
+                     "frac": round(achieved / peak, 4),
+                     "traffic": int(algo_bytes * DRAM_TRAFFIC_OVER_ALGORITHMIC),
+                     "traffic_note": "bytes per step (4 launches): ncu dram read+write of one launch / its algorithmic "
+                                     "bytes = 1.015, applied to the step", "peak_source": peak_kind,
                      "kernel": "spmm_decode_kernel<16>", "algorithmic_bytes_per_step": algo_bytes},
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(2 * L["K"] * N_TOKENS for L in layers),
