@@ -1,0 +1,82 @@
+"""Tensor-parallel use of the SpMM: how one layer's weights are split over the GPUs of a box.
+
+The reference itself is single-GPU; its weight-conversion tool shards every layer offline and
+FasterTransformer adds the collective (end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:134-135:
+QKV and FFN1 are split by output rows M, out-proj and FFN2 by K).  The same two splits here:
+
+* column-parallel (by rows of A): tiles are emitted row-of-tiles major (csrc/SpMM_API.cu:313-314),
+  so the rows of rank r are a contiguous slice of the words and offsets of the whole matrix --
+  `row_shard` cuts it out, bit-identical to encoding the shard alone.  B is replicated, every rank
+  produces its own rows of C, no collective.
+* row-parallel (by K): rank r owns columns [r*K/g, (r+1)*K/g) of A and the matching rows of B.  The
+  columns are not contiguous in the encoded stream, so each shard is encoded from its dense slice
+  (`column_slice`).  Every rank produces a full-size partial C; one sum all-reduce finishes it.
+
+One process per GPU; `torch.distributed` (NCCL on GPUs, gloo in the CPU tests) carries the reduce.
+"""
+import numpy as np
+
+TILE_M = 128
+TILE_K = 64
+
+
+def row_shard(words, offsets, M, K, rank, world):
+    """Words and offsets of rows [rank*M/world, (rank+1)*M/world) cut from the encoding of the whole matrix.
+
+    Returns (words, offsets, M_shard).  M/world must be a multiple of 128."""
+    if M % (world * TILE_M) != 0:
+        raise ValueError("M / world must be a multiple of %d" % TILE_M)
+    tiles_k = K // TILE_K
+    rows_of_tiles = M // TILE_M // world
+    t0, t1 = rank * rows_of_tiles * tiles_k, (rank + 1) * rows_of_tiles * tiles_k
+    offs = np.asarray(offsets[t0:t1 + 1], dtype=np.int64)
+    shard_offsets = np.concatenate([offs - offs[0], [offs[-1] - offs[0]]]).astype(np.int32)  # duplicated tail entry
+    shard_words = np.ascontiguousarray(words[int(offs[0]) * 4:int(offs[-1]) * 4])
+    return shard_words, shard_offsets, rows_of_tiles * TILE_M
+
+
+def column_slice(A, rank, world):
+    """Dense columns [rank*K/world, (rank+1)*K/world) of A, contiguous, ready for the encoder."""
+    K = A.shape[1]
+    if K % (world * TILE_K) != 0:
+        raise ValueError("K / world must be a multiple of %d" % TILE_K)
+    k = K // world
+    return np.ascontiguousarray(A[:, rank * k:(rank + 1) * k])
+
+
+def activation_rows(B, rank, world):
+    """Rows [rank*K/world, (rank+1)*K/world) of B[K][N]: the activations a row-parallel rank multiplies."""
+    K = B.shape[0]
+    k = K // world
+    return np.ascontiguousarray(B[rank * k:(rank + 1) * k])
+
+
+def all_reduce_partial(C_partial, group=None):
+    """Sum of the ranks' partial results, in place.  C_partial: torch tensor (fp16 or fp32) on the
+    device of the process group's backend."""
+    import torch.distributed as dist
+    if dist.is_initialized() and dist.get_world_size(group) > 1:
+        dist.all_reduce(C_partial, op=dist.ReduceOp.SUM, group=group)
+    return C_partial
+
+
+class RowParallelSpMM:
+    """One rank's part of a row-parallel layer on its GPU: SpMM over its K shard, then the all-reduce."""
+
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8):
+        import torch
+        from . import spmm_api
+        self._api = spmm_api
+        self.words, self.offsets = words_dev, offsets_dev
+        self.M, self.N, self.K = M, N, K_shard
+        self.split_k = split_k
+        dev = words_dev.device
+        self.C = torch.zeros((M, N), dtype=torch.float16, device=dev)
+        self.workspace = torch.zeros(spmm_api.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
+
+    def forward(self, B_shard_dev, group=None):
+        rc = self._api.SpMM_SplitK_API(None, None, self.words, None, None, self.offsets, B_shard_dev, self.C, self.M,
+                                       self.N, self.K, self.workspace, self.split_k)
+        if rc != 0:
+            raise RuntimeError("SpMM_SplitK_API failed with cudaError %d" % rc)
+        return all_reduce_partial(self.C, group)

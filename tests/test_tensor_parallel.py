@@ -1,0 +1,117 @@
+"""Tensor-parallel splits of one layer: column-parallel by rows of A (no collective) and
+row-parallel by K (one sum all-reduce).  The CPU tests run two gloo ranks with the oracle as the
+local product; the GPU test runs two NCCL ranks on two GPUs through the CUDA SpMM."""
+import os
+import socket
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_row_shards_are_slices_of_the_whole_encoding(sp):
+    from graphneuralnetproj_b200 import tensor_parallel as tp
+    M, K = 1024, 512
+    A = sp.synth_fp16((M, K), 5, 0.02, 0.8)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, 16, K)
+    for world in (1, 2, 4, 8):
+        for rank in range(world):
+            w, o, m = tp.row_shard(words, offsets, M, K, rank, world)
+            rows = A[rank * m:(rank + 1) * m]
+            w_alone, o_alone, _ = sp.InitSparseMatrixA_API(rows, m, 16, K)
+            assert m == M // world and np.array_equal(w, w_alone) and np.array_equal(o, o_alone)
+    with pytest.raises(ValueError):
+        tp.row_shard(words, offsets, M, K, 0, 3)
+
+
+WORKER = r"""
+import os, sys
+import numpy as np
+import torch
+import torch.distributed as dist
+sys.path.insert(0, {root!r})
+import graphneuralnetproj_b200 as sp
+from graphneuralnetproj_b200 import tensor_parallel as tp
+import oracle
+backend, mode = sys.argv[1], sys.argv[2]
+rank, world = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"])
+if backend == "nccl":
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", device_id=torch.device("cuda", rank))
+else:
+    dist.init_process_group("gloo")
+M, K, N = 1024, 2048, 16
+A = sp.synth_fp16((M, K), 11, 0.02, 0.8)
+B = sp.synth_fp16((K, N), 12, 1.0, 0.0)
+C64 = oracle.spmm_f64(A, B)
+if mode == "column":
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    w, o, m = tp.row_shard(words, offsets, M, K, rank, world)
+    if backend == "nccl":
+        dev = torch.device("cuda", rank)
+        Cd = torch.zeros((m, N), dtype=torch.int16, device=dev)
+        ws = torch.zeros(sp.workspace_bytes(m, N, 8) // 2, dtype=torch.int16, device=dev)
+        rc = sp.SpMM_SplitK_API(None, None, torch.from_numpy(np.concatenate([w, np.zeros(4, np.uint32)]).view(np.int32)).to(dev), None, None,
+                                torch.from_numpy(o).to(dev), torch.from_numpy(B.view(np.int16)).to(dev), Cd, m, N, K, ws, 8)
+        torch.cuda.synchronize(); assert rc == 0 and sp.device_status() == 0
+        mine = Cd.cpu().numpy().view(np.uint16)
+    else:
+        mine = oracle.spmm_from_csl(w, o, B, m, K)
+    ok, mx, mr = oracle.tolerance_check(mine, C64[rank * m:(rank + 1) * m])
+    assert ok, (mx, mr)
+    # no collective on the data path: only the verdicts are gathered
+    flag = torch.tensor([1 if ok else 0], device="cuda" if backend == "nccl" else "cpu")
+    dist.all_reduce(flag)
+    assert int(flag.item()) == world
+else:
+    As, Bs = tp.column_slice(A, rank, world), tp.activation_rows(B, rank, world)
+    k = K // world
+    w, o, _ = sp.InitSparseMatrixA_API(As, M, N, k)
+    if backend == "nccl":
+        dev = torch.device("cuda", rank)
+        layer = tp.RowParallelSpMM(torch.from_numpy(np.concatenate([w, np.zeros(4, np.uint32)]).view(np.int32)).to(dev),
+                                   torch.from_numpy(o).to(dev), M, N, k)
+        C = layer.forward(torch.from_numpy(Bs.view(np.int16)).to(dev))
+        torch.cuda.synchronize(); assert sp.device_status() == 0
+        total = C.cpu().numpy().view(np.uint16)
+    else:
+        part = torch.from_numpy(oracle.spmm_from_csl(w, o, Bs, M, k).view(np.float16).astype(np.float32))
+        total = tp.all_reduce_partial(part).numpy().astype(np.float16).view(np.uint16)
+    ok, mx, mr = oracle.tolerance_check(total, C64)
+    assert ok, (mx, mr)
+dist.barrier()
+dist.destroy_process_group()
+print("rank", rank, "ok")
+"""
+
+
+def run_ranks(world, backend, mode):
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        port = s.getsockname()[1]
+    procs = []
+    for rank in range(world):
+        env = dict(os.environ, RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank), MASTER_ADDR="127.0.0.1",
+                   MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+        procs.append(subprocess.Popen([sys.executable, "-c", WORKER.format(root=ROOT), backend, mode], env=env,
+                                      stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True))
+    outs = [p.communicate(timeout=600)[0] for p in procs]
+    for p, out in zip(procs, outs):
+        assert p.returncode == 0, out[-3000:]
+
+
+@pytest.mark.parametrize("mode", ["column", "row"])
+def test_two_gloo_ranks_on_cpu(mode):
+    run_ranks(2, "gloo", mode)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("mode", ["column", "row"])
+def test_two_nccl_ranks_on_gpus(mode):
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    run_ranks(2, "nccl", mode)
