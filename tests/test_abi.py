@@ -11,6 +11,12 @@ CXX_SYMBOLS = [
     "_Z15SpMM_SplitK_APIP11CUstream_stPK6__halfPK5uint4PKmPKiSA_S3_PS1_iiiSB_i",
     "_Z21InitSparseMatrixA_APIP6__halfiiiPPjPPi",
     "_Z31InitSparseMatrixA_API_NoReorderP6__halfiiiPPjPPi",
+    "_Z34InitSparseMatrixA_API_NoReorder_v1P6__halfiiiPPjPPi",
+    "_Z34InitSparseMatrixA_API_NoReorder_v2P6__halfiiiPS0_PPi",
+    "_Z34InitSparseMatrixA_API_NoReorder_v3P6__halfiiiPS0_PPi",
+    "_Z34InitSparseMatrixA_API_NoReorder_v4P6__halfiiiPS0_PPi",
+    "_Z34InitSparseMatrixA1_Vec_Sparse_LoadP6__halfiiPS0_PPmPPi",
+    "_Z16inspect_metadataP6__halfPiii",
 ]
 
 
