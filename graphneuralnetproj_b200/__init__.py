@@ -8,6 +8,7 @@ from .spmm_api import (  # noqa: F401
     InitSparseMatrixA_API,
     InitSparseMatrixA_API_NoReorder,
     SpMM_SplitK_API,
+    SpMM_SplitK_API_token_major,
     decompose,
     device_status,
     plan,

@@ -26,7 +26,7 @@ struct DecodeConfig {
 
 struct DeviceInfo {
     int  sm_count = 0;
-    bool attrs_set[4] = {false, false, false, false};
+    bool attrs_set[8] = {false, false, false, false, false, false, false, false};
 };
 
 DeviceInfo& device_info(int device)
@@ -107,11 +107,11 @@ cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, in
 }
 #endif
 
-template<int N>
+template<int N, int TM = 0>
 cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, const DecodeParams& params)
 {
 #ifdef SPMM_B200_ABLATIONS
-    if (N == 16) {
+    if (N == 16 && !TM) {
         const char* env = getenv("SPMM_B200_ABLATE");
         const char* envd = getenv("SPMM_B200_D");
         const int abl = env ? atoi(env) : 0;
@@ -133,7 +133,7 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
     constexpr int smem = decode_smem_bytes<NB, D>();
-    auto          kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL>;
+    auto          kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, 0, TM>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -154,38 +154,26 @@ bool aligned16(const void* p)
 }  // namespace
 }  // namespace spmm_b200
 
-cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
-                            const half*     A,
-                            const uint4*    Compressed_A,
-                            const uint64_t* A1_Ind_data,
-                            const int*      metadata,
-                            const int*      TileOffsets,
-                            const half*     B,
-                            half*           C,
-                            const int       M_Global,
-                            const int       N_Global,
-                            const int       K_Global,
-                            half*           Reduction_Workspace,
-                            int             Split_K)
+namespace spmm_b200 {
+namespace {
+
+// Shared by both layouts: validates, partitions, launches.  token_major: B[N][K], C[N][M].
+cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const int* TileOffsets, const half* B, half* C,
+                           int M_Global, int N_Global, int K_Global, half* Reduction_Workspace, int Split_K, bool token_major)
 {
-    using namespace spmm_b200;
-    (void)A;
-    (void)A1_Ind_data;
     if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
         return cudaErrorUnknown;
     }
-    if (metadata != nullptr)
-        return cudaErrorNotSupported;  // structured (2:4) half: not handled by this kernel
     if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kTileCols != 0
         || M_Global / kTileRows > kMaxRowTiles || Split_K < 1)
         return cudaErrorInvalidValue;
-    if (!Compressed_A || !TileOffsets || !B || !C || !aligned16(Compressed_A) || !aligned16(B) || !aligned16(C)
-        || !aligned16(Reduction_Workspace))
+    if (!Compressed_A || !TileOffsets || !B || !C || !aligned16(Compressed_A) || !aligned16(B)
+        || !aligned16(Reduction_Workspace) || (!token_major && !aligned16(C)))
         return cudaErrorInvalidValue;
 
-    int device = 0;
-    cudaError_t e = cudaGetDevice(&device);
+    int         device = 0;
+    cudaError_t e      = cudaGetDevice(&device);
     if (e != cudaSuccess)
         return e;
     DeviceInfo& dev = device_info(device);
@@ -203,7 +191,20 @@ cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
     params.slots        = reinterpret_cast<float*>(Reduction_Workspace);
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
+    params.m            = M_Global;
     params.sched        = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, slots});
+    if (token_major) {
+        switch (N_Global) {
+            case 8:
+                return launch_decode<8, 1>(stream, dev, 4, params);
+            case 16:
+                return launch_decode<16, 1>(stream, dev, 5, params);
+            case 32:
+                return launch_decode<32, 1>(stream, dev, 6, params);
+            default:
+                return launch_decode<64, 1>(stream, dev, 7, params);
+        }
+    }
     switch (N_Global) {
         case 8:
             return launch_decode<8>(stream, dev, 0, params);
@@ -214,6 +215,53 @@ cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
         default:
             return launch_decode<64>(stream, dev, 3, params);
     }
+}
+
+}  // namespace
+}  // namespace spmm_b200
+
+cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
+                            const half*     A,
+                            const uint4*    Compressed_A,
+                            const uint64_t* A1_Ind_data,
+                            const int*      metadata,
+                            const int*      TileOffsets,
+                            const half*     B,
+                            half*           C,
+                            const int       M_Global,
+                            const int       N_Global,
+                            const int       K_Global,
+                            half*           Reduction_Workspace,
+                            int             Split_K)
+{
+    (void)A;
+    (void)A1_Ind_data;
+    if (metadata != nullptr) {
+        if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
+            printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
+            return cudaErrorUnknown;
+        }
+        return cudaErrorNotSupported;  // structured (2:4) half: not handled by this kernel
+    }
+    return spmm_b200::spmm_tiled_csl(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,
+                                     Reduction_Workspace, Split_K, false);
+}
+
+cudaError_t SpMM_SplitK_API(cudaStream_t stream,
+                            const half*  A,
+                            const uint4* Compressed_A,
+                            const int*   TileOffsets,
+                            const half*  B,
+                            half*        C,
+                            const int    M_Global,
+                            const int    N_Global,
+                            const int    K_Global,
+                            half*        Reduction_Workspace,
+                            int          Split_K)
+{
+    (void)A;
+    return spmm_b200::spmm_tiled_csl(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,
+                                     Reduction_Workspace, Split_K, true);
 }
 
 // ------------------------------------------------------------------ entry point that allocates nothing
@@ -302,6 +350,7 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
     params.slots        = scratch;
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
+    params.m            = M_Global;
     params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, static_cast<long>(kOwnScratchBytes / slot_bytes)});
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (N_Global) {
@@ -379,6 +428,23 @@ int spmm_b200_spmm_splitk(void*       stream,
                                             K_Global,
                                             static_cast<half*>(Reduction_Workspace),
                                             Split_K));
+}
+
+int spmm_b200_spmm_splitk_token_major(void*       stream,
+                                      const void* Compressed_A,
+                                      const int*  TileOffsets,
+                                      const void* B,
+                                      void*       C,
+                                      int         M_Global,
+                                      int         N_Global,
+                                      int         K_Global,
+                                      void*       Reduction_Workspace,
+                                      int         Split_K)
+{
+    return static_cast<int>(SpMM_SplitK_API(static_cast<cudaStream_t>(stream), nullptr,
+                                            static_cast<const uint4*>(Compressed_A), TileOffsets,
+                                            static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global,
+                                            K_Global, static_cast<half*>(Reduction_Workspace), Split_K));
 }
 
 size_t spmm_b200_workspace_bytes(int M_Global, int N_Global, int Split_K)

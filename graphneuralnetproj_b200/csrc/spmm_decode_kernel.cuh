@@ -88,6 +88,7 @@ struct DecodeParams {
     float*       slots;         // fp32 partial tiles, 128 * N floats each
     int          n;             // N (8, 16, 32 or 64)
     int          tiles_k;       // K / 64
+    int          m;             // M, used by the token-major layout only
     Schedule     sched;
 };
 
@@ -145,7 +146,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 //         Decoders that share the load/store unit evenly all finish together and then all wait for
 //         their MMAs together, so the store phase and the MMA round trip add up instead of
 //         overlapping; taking turns keeps the hand-overs staggered.
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TURNS = 0>
+// TM : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
+//      library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
+//      k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TURNS = 0, int TM = 0>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
@@ -233,8 +237,21 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         auto stage_b = [&](int j, int parity) {
             if (ABL & 16)
                 return;
-            const uint4*   b_src = reinterpret_cast<const uint4*>(p.B) + static_cast<size_t>(j) * kChunks + first_chunk;
-            const uint32_t dst   = b_base + (parity * D + s_own) * BT::kBytes;
+            const uint32_t dst = b_base + (parity * D + s_own) * BT::kBytes;
+            if (TM) {
+                // row n of the slice: 64 halves of token n starting at column 64 j (eight 16-byte chunks);
+                // chunk q of row n lands at n * 128 + ((q ^ (n % 8)) * 16)
+                const half* b_src = p.B + static_cast<size_t>(j) * kTileCols;
+#pragma unroll
+                for (int i = 0; i < (N * 8) / (WPT * 32); i++) {
+                    const uint32_t c = first_chunk + i * WPT * 32;
+                    const uint32_t n = c >> 3, q = c & 7;
+                    ptx::cp_async_16(dst + n * 128u + ((q ^ (n & 7u)) << 4),
+                                     b_src + static_cast<size_t>(n) * (static_cast<size_t>(tiles_k) * kTileCols) + q * 8);
+                }
+                return;
+            }
+            const uint4* b_src = reinterpret_cast<const uint4*>(p.B) + static_cast<size_t>(j) * kChunks + first_chunk;
 #pragma unroll
             for (int i = 0; i < kChunks / (WPT * 32); i++) {
                 const uint32_t c   = first_chunk + i * WPT * 32;
@@ -383,9 +400,11 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // issued anything for the segment and directly otherwise.
         const int q = warp - kFirstMmaWarp;
         if (lane == 0) {
-            constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(kTileRows, NB, false, true);
+            constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(kTileRows, NB, false, TM ? false : true);
             const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
-            const uint64_t     b_desc0 = ptx::make_smem_desc(b_base, BT::kGroupBytes, BT::kGroupBytes, BT::kSwizzleMode);
+            const uint64_t     b_desc0 =
+                TM ? ptx::make_smem_desc(b_base, 16, 1024, ptx::kSwizzle128B)
+                   : ptx::make_smem_desc(b_base, BT::kGroupBytes, BT::kGroupBytes, BT::kSwizzleMode);
             bool ok  = true;
             int  seg = 0;
 #pragma unroll 1
@@ -412,7 +431,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         // A: 16 k values = 32 bytes along the swizzled row; B: 16 k rows = two 8-row groups.
                         ptx::umma_f16_ss(d_tmem,
                                          a_desc + static_cast<uint64_t>((k * 32) >> 4),
-                                         b_desc + static_cast<uint64_t>((k * 2 * BT::kGroupBytes) >> 4),
+                                         b_desc + static_cast<uint64_t>((TM ? k * 32 : k * 2 * BT::kGroupBytes) >> 4),
                                          idesc,
                                          k == 0 ? accumulate : 1u);
                     }
@@ -529,7 +548,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     write_c = true;
                 }
             }
-            if (write_c) {
+            if (write_c && TM) {
+                half* dst = p.C + static_cast<size_t>(row_tile) * kTileRows + row_in_tile;  // C[n][m]
+#pragma unroll
+                for (int n = 0; n < N; n++)
+                    dst[static_cast<size_t>(n) * p.m] = __float2half_rn(acc[n]);
+            }
+            else if (write_c) {
                 uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * N);
 #pragma unroll
                 for (int c = 0; c < N / 8; c++) {

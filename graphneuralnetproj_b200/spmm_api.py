@@ -43,6 +43,8 @@ def _load():
     lib.spmm_b200_spmm_splitk.restype = ctypes.c_int
     lib.spmm_b200_spmm_own_scratch.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3
     lib.spmm_b200_spmm_own_scratch.restype = ctypes.c_int
+    lib.spmm_b200_spmm_splitk_token_major.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
+    lib.spmm_b200_spmm_splitk_token_major.restype = ctypes.c_int
     lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
     for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):
@@ -128,6 +130,19 @@ def SpMM_SplitK_API(stream, A, Compressed_A, A1_Ind_data, metadata, TileOffsets,
     return LIB.spmm_b200_spmm_splitk(ctypes.c_void_p(handle), _dev_ptr(A), _dev_ptr(Compressed_A), _dev_ptr(A1_Ind_data),
                                      _dev_ptr(metadata), _dev_ptr(TileOffsets), _dev_ptr(B), _dev_ptr(C), M_Global,
                                      N_Global, K_Global, _dev_ptr(Reduction_Workspace), Split_K)
+
+
+def SpMM_SplitK_API_token_major(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,
+                                Reduction_Workspace, Split_K):
+    """The upstream eleven-argument form the FasterTransformer glue calls (third_party/ft.patch:2822-2846):
+    token-major activations B[N][K] and results C[N][M]."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    handle = stream if isinstance(stream, int) else stream.cuda_stream
+    return LIB.spmm_b200_spmm_splitk_token_major(ctypes.c_void_p(handle), _dev_ptr(Compressed_A), _dev_ptr(TileOffsets),
+                                                 _dev_ptr(B), _dev_ptr(C), M_Global, N_Global, K_Global,
+                                                 _dev_ptr(Reduction_Workspace), Split_K)
 
 
 def spmm_own_scratch(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global):

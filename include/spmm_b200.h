@@ -49,6 +49,19 @@ int spmm_b200_spmm_splitk(void*       stream,
                           void*       Reduction_Workspace,
                           int         Split_K);
 
+/* The eleven-argument upstream form of SpMM_SplitK_API that the reference's FasterTransformer
+ * glue calls (third_party/ft.patch:2822-2846), with token-major layouts: B[N][K], C[N][M]. */
+int spmm_b200_spmm_splitk_token_major(void*       stream,
+                                      const void* Compressed_A,
+                                      const int*  TileOffsets,
+                                      const void* B,
+                                      void*       C,
+                                      int         M_Global,
+                                      int         N_Global,
+                                      int         K_Global,
+                                      void*       Reduction_Workspace,
+                                      int         Split_K);
+
 /* SpMM for callers that can neither allocate device memory nor bring a workspace: a plugin or
  * serving callback that is handed only the tensors of the call, a host that has frozen its
  * allocator after start-up, a latency-critical loop in which cudaMalloc's implicit

@@ -160,3 +160,28 @@ def test_error_paths(sp, torch_cuda, capfd):
     assert sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, 16, K, ws, 4) == 0
     torch.cuda.synchronize()
     assert sp.device_status() == 0
+
+
+@pytest.mark.parametrize("case", [(256, 192, 8, 0.8), (1024, 2048, 16, 0.8), (2304, 4608, 32, 0.7), (1152, 1024, 64, 0.9)],
+                         ids=["N8", "N16", "N32", "N64"])
+def test_token_major_layout(sp, oracle, torch_cuda, case):
+    """The upstream eleven-argument form (third_party/ft.patch:2822-2846): B[N][K], C[N][M]."""
+    torch = torch_cuda
+    dev = torch.device("cuda:0")
+    M, K, N, p = case
+    A = sp.synth_fp16((M, K), 300 + N, 0.02, p)
+    B = sp.synth_fp16((K, N), 400 + N, 1.0, 0.0)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    od = torch.from_numpy(offsets).to(dev)
+    Bt = torch.from_numpy(np.ascontiguousarray(B.T).view(np.int16)).to(dev)          # [N][K]
+    Ct = torch.full((N, M), 0x7E00, dtype=torch.int16, device=dev)                   # [N][M]
+    ws = torch.zeros(sp.workspace_bytes(M, N, 8) // 2, dtype=torch.int16, device=dev)
+    assert sp.SpMM_SplitK_API_token_major(None, wd, od, Bt, Ct, M, N, K, ws, 8) == 0
+    torch.cuda.synchronize()
+    assert sp.device_status() == 0
+    C = np.ascontiguousarray(Ct.cpu().numpy().view(np.uint16).T)
+    ok, max_ratio, mean_rel = oracle.tolerance_check(C, oracle.spmm_f64(A, B))
+    assert ok, (max_ratio, mean_rel)
+    # same accumulation as the row-major entry point: bitwise equal results
+    assert np.array_equal(C, run_spmm(sp, torch, words, offsets, B, M, N, K, 8))
