@@ -355,6 +355,74 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_sweep(args):
+    """Decode-size sweep over the OPT-66B layer shapes, N and sparsity (one JSON line per point),
+    with cuBLAS dense fp16 on the pruned matrix as the comparator.  Device-timed with CUDA graphs;
+    every shape's weights exceed or rotate through L2 (copies chosen so that the set is >= 256 MB)."""
+    import torch
+
+    import graphneuralnetproj_b200 as sp
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    peak, _ = measured_hbm_peak()
+    shapes = [(n, m, k) for n, m, k, _ in LAYERS]
+    n_list = [int(x) for x in args.sweep_n.split(",")]
+    p_list = [float(x) for x in args.sweep_p.split(",")]
+    for name, M, K in shapes:
+        for p in p_list:
+            A = sp.synth_fp16((M, K), 0xA100 + int(p * 100), 0.02, p)
+            words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, 16, K)
+            wbytes = 4 * words.size + 4 * n_offsets
+            copies = max(1, int(np.ceil(256e6 / wbytes)))
+            wds = [torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+                   for _ in range(copies)]
+            od = torch.from_numpy(offsets).to(dev)
+            dense = [torch.from_numpy(A.view(np.float16)).to(dev) for _ in range(max(1, min(copies, 2)))]
+            del A, words
+            for N in n_list:
+                Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB100, 1.0).view(np.int16)).to(dev)
+                Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
+                ws = torch.zeros(sp.workspace_bytes(M, N, 8) // 2, dtype=torch.int16, device=dev)
+
+                def ours(i):
+                    rc = sp.SpMM_SplitK_API(None, None, wds[i % copies], None, None, od, Bd, Cd, M, N, K, ws, 8)
+                    assert rc == 0, rc
+
+                def cublas(i):
+                    torch.matmul(dense[i % len(dense)], Bd.view(torch.float16))
+
+                times = {}
+                for label, fn in (("spmm", ours), ("cublas_dense", cublas)):
+                    stream = torch.cuda.Stream()
+                    with torch.cuda.stream(stream):
+                        for i in range(4):
+                            fn(i)
+                        torch.cuda.synchronize()
+                        g = torch.cuda.CUDAGraph()
+                        reps = 12
+                        with torch.cuda.graph(g, stream=stream):
+                            for i in range(reps):
+                                fn(i)
+                        g.replay()
+                        torch.cuda.synchronize()
+                        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                        e0.record(stream)
+                        for _ in range(5):
+                            g.replay()
+                        e1.record(stream)
+                        torch.cuda.synchronize()
+                        times[label] = e0.elapsed_time(e1) * 1000.0 / (5 * reps)
+                algo = algorithmic_bytes(wbytes // 4 - n_offsets, n_offsets, M, K, N)
+                print(json.dumps({"layer": name, "M": M, "K": K, "N": N, "sparsity": p,
+                                  "spmm_us": round(times["spmm"], 2), "cublas_dense_us": round(times["cublas_dense"], 2),
+                                  "speedup_vs_cublas": round(times["cublas_dense"] / times["spmm"], 3),
+                                  "weight_gbs": round(wbytes / times["spmm"] / 1e3, 1),
+                                  "roofline_frac": round(algo / times["spmm"] / 1e3 / peak, 4)}), flush=True)
+            del wds, dense
+            torch.cuda.empty_cache()
+    assert sp.device_status() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -362,8 +430,13 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--sweep", action="store_true", help="decode-size sweep (layers x N x sparsity) instead of the bench line")
+    ap.add_argument("--sweep-n", default="8,16,32,64")
+    ap.add_argument("--sweep-p", default="0.7,0.8,0.9")
     args = ap.parse_args()
-    if args.impl == "reference":
+    if args.sweep:
+        run_sweep(args)
+    elif args.impl == "reference":
         run_reference(args)
     else:
         run_ours(args)

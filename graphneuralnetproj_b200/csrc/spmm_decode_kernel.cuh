@@ -356,10 +356,15 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     if (lane_vec + v * WPT * 32 < nvec)
                         ptx::scatter_words(a_tile, r[v]);
             }
-            if (nvec > VPL * WPT * 32) {  // denser than the register budget: stream the rest
+            // Tiles denser than the register budget (VPL * WPT * 32 vectors): the rest follows in further
+            // register batches; the tile was requested into L2 two rounds ago, so these loads are short.
 #pragma unroll 1
-                for (int idx = lane_vec + VPL * WPT * 32; idx < nvec; idx += WPT * 32)
-                    ptx::scatter_words(a_tile, ptx::ld_stream_128(src - lane_vec + idx));
+            for (int done = VPL * WPT * 32; done < nvec; done += VPL * WPT * 32) {
+                load_words(src + done, nvec - done);
+#pragma unroll
+                for (int v = 0; v < VPL; v++)
+                    if (lane_vec + v * WPT * 32 < nvec - done)
+                        ptx::scatter_words(a_tile, r[v]);
             }
             if (TURNS > 0) {
                 __syncwarp();
