@@ -423,6 +423,57 @@ def run_sweep(args):
     assert sp.device_status() == 0
 
 
+def run_prefill(args):
+    """Prefill-size points (N >= 256): dense-equivalent TFLOP/s = 2*M*N*K / t against the measured
+    dense tensor peak, with cuBLAS dense fp16 beside it.  One JSON line per point."""
+    import torch
+
+    import graphneuralnetproj_b200 as sp
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            tensor_peak = float(json.load(f)["bf16_tflops"])
+    except Exception:
+        tensor_peak = 1590.0
+    shapes = [(12288, 12288), (49152, 12288)] if not args.small else [(12288, 12288)]
+    for M, K in shapes:
+        for p in [float(x) for x in args.sweep_p.split(",")]:
+            A = sp.synth_fp16((M, K), 0xA300 + int(p * 100), 0.02, p)
+            words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, 64, K)
+            wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+            od = torch.from_numpy(offsets).to(dev)
+            Ad = torch.from_numpy(A.view(np.float16)).to(dev)
+            del A, words
+            for N in [int(x) for x in args.prefill_n.split(",")]:
+                Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB300, 1.0).view(np.int16)).to(dev)
+                Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
+                ws = torch.zeros(sp.workspace_bytes(M, N, 2) // 2, dtype=torch.int16, device=dev)
+                times = {}
+                for label, fn in (("spmm", lambda: sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 2)),
+                                  ("cublas_dense", lambda: torch.matmul(Ad, Bd.view(torch.float16)))):
+                    for _ in range(3):
+                        fn()
+                    torch.cuda.synchronize()
+                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                    reps = 5
+                    e0.record()
+                    for _ in range(reps):
+                        fn()
+                    e1.record()
+                    torch.cuda.synchronize()
+                    times[label] = e0.elapsed_time(e1) * 1000.0 / reps
+                flops = 2.0 * M * N * K
+                print(json.dumps({"M": M, "K": K, "N": N, "sparsity": p, "spmm_us": round(times["spmm"], 1),
+                                  "cublas_dense_us": round(times["cublas_dense"], 1),
+                                  "dense_equiv_tflops": round(flops / times["spmm"] / 1e6, 1),
+                                  "frac_of_tensor_peak": round(flops / times["spmm"] / 1e6 / tensor_peak, 4),
+                                  "tensor_peak_tflops": tensor_peak}), flush=True)
+            del wd, Ad
+            torch.cuda.empty_cache()
+    assert sp.device_status() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -433,8 +484,13 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="decode-size sweep (layers x N x sparsity) instead of the bench line")
     ap.add_argument("--sweep-n", default="8,16,32,64")
     ap.add_argument("--sweep-p", default="0.7,0.8,0.9")
+    ap.add_argument("--prefill", action="store_true", help="prefill-size points (N >= 256) instead of the bench line")
+    ap.add_argument("--prefill-n", default="256,512,1024,2048")
+    ap.add_argument("--small", action="store_true", help="with --prefill: only the 12288 x 12288 shape")
     args = ap.parse_args()
-    if args.sweep:
+    if args.prefill:
+        run_prefill(args)
+    elif args.sweep:
         run_sweep(args)
     elif args.impl == "reference":
         run_reference(args)

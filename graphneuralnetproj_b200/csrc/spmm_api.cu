@@ -1,6 +1,7 @@
 // Launcher and dispatcher: the sm_100a counterpart of SpMM_SplitK_API /
 // SpMM_SplitK_Kernel_Ex (csrc/SpMM_API.cu:25-208), plus the extern "C" views
 // declared in include/spmm_b200.h.
+#include <algorithm>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -108,7 +109,8 @@ cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, in
 #endif
 
 template<int N, int TM = 0>
-cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, const DecodeParams& params)
+cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, const DecodeParams& params,
+                          int column_blocks = 1)
 {
 #ifdef SPMM_B200_ABLATIONS
     if (N == 16 && !TM) {
@@ -142,7 +144,7 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
         }
         dev.attrs_set[n_index] = true;
     }
-    kern<<<params.sched.num_ctas, decode_threads<D, Cfg::Q, Cfg::WPT>(), smem, stream>>>(params);
+    kern<<<dim3(params.sched.num_ctas, column_blocks), decode_threads<D, Cfg::Q, Cfg::WPT>(), smem, stream>>>(params);
     return cudaGetLastError();
 }
 
@@ -161,12 +163,17 @@ namespace {
 cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const int* TileOffsets, const half* B, half* C,
                            int M_Global, int N_Global, int K_Global, half* Reduction_Workspace, int Split_K, bool token_major)
 {
-    if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
+    // N: 8, 16, 32, 64 as in the reference (csrc/SpMM_API.cu:105-196); multiples of 64 beyond that are
+    // served by the same kernel, one 64-column block per blockIdx.y (row-major layout only).
+    const bool wide = N_Global > 64 && N_Global % 64 == 0 && N_Global <= 8192 && !token_major;
+    if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64 && !wide) {
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
         return cudaErrorUnknown;
     }
+    const int column_blocks = wide ? N_Global / 64 : 1;
+    const int n_block       = wide ? 64 : N_Global;
     if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kTileCols != 0
-        || M_Global / kTileRows > kMaxRowTiles || Split_K < 1)
+        || static_cast<long>(M_Global / kTileRows) * column_blocks > kMaxRowTiles || Split_K < 1)
         return cudaErrorInvalidValue;
     if (!Compressed_A || !TileOffsets || !B || !C || !aligned16(Compressed_A) || !aligned16(B)
         || !aligned16(Reduction_Workspace) || (!token_major && !aligned16(C)))
@@ -179,9 +186,10 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     DeviceInfo& dev = device_info(device);
 
     const int  tiles_m = M_Global / kTileRows, tiles_k = K_Global / kTileCols;
+    // every column block gets an equal share of the workspace for its partial tiles
     const long slots   = Reduction_Workspace
                              ? static_cast<long>(static_cast<size_t>(Split_K) * M_Global * N_Global * sizeof(half)
-                                                 / (static_cast<size_t>(kTileRows) * N_Global * sizeof(float)))
+                                                 / (static_cast<size_t>(kTileRows) * n_block * sizeof(float)) / column_blocks)
                              : 0;
     DecodeParams params;
     params.words        = Compressed_A;
@@ -192,7 +200,12 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
     params.m            = M_Global;
-    params.sched        = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, slots});
+    params.ld           = N_Global;
+    // with several column blocks the blocks of one column share the SMs with the other columns
+    params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots});
+    params.slots_per_block_column = params.sched.slots_used;
+    if (wide)
+        return launch_decode<64>(stream, dev, 3, params, column_blocks);
     if (token_major) {
         switch (N_Global) {
             case 8:
@@ -315,9 +328,10 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
                kTileRows, K_Global, kTileCols);
         return static_cast<int>(cudaErrorInvalidValue);
     }
-    if (M_Global / kTileRows > kMaxRowTiles) {
+    constexpr int kOwnScratchMaxRowTiles = 8192;
+    if (M_Global / kTileRows > kOwnScratchMaxRowTiles) {
         printf("spmm_b200_spmm_own_scratch: M = %d exceeds the supported maximum of %d rows\n", M_Global,
-               kMaxRowTiles * kTileRows);
+               kOwnScratchMaxRowTiles * kTileRows);
         return static_cast<int>(cudaErrorInvalidValue);
     }
     if (!Compressed_A || !TileOffsets || !B || !C || !aligned16(Compressed_A) || !aligned16(B) || !aligned16(C))
@@ -351,6 +365,8 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
     params.m            = M_Global;
+    params.ld           = N_Global;
+    params.slots_per_block_column = 0;
     params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, static_cast<long>(kOwnScratchBytes / slot_bytes)});
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (N_Global) {

@@ -54,7 +54,7 @@ constexpr int kTileCols        = 64;   // k extent of an encoded tile
 constexpr int kATileBytes      = kTileRows * kTileCols * 2;
 constexpr int kEpilogueWarps   = 4;
 constexpr int kFirstMmaWarp    = 4;
-constexpr int kMaxRowTiles     = 8192;  // arrival counters are sized for M <= 128 * 8192
+constexpr int kMaxRowTiles     = 32768;  // arrival counters: rows of tiles x 64-column blocks per launch
 
 enum DeviceStatus : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
 
@@ -88,7 +88,9 @@ struct DecodeParams {
     float*       slots;         // fp32 partial tiles, 128 * N floats each
     int          n;             // N (8, 16, 32 or 64)
     int          tiles_k;       // K / 64
-    int          m;             // M, used by the token-major layout only
+    int          m;             // M
+    int          ld;            // row stride of B[K][ld] and C[M][ld] in halves (row-major layout): the full N
+    int          slots_per_block_column;  // workspace slots used by one column block (blockIdx.y)
     Schedule     sched;
 };
 
@@ -251,12 +253,14 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 }
                 return;
             }
-            const uint4* b_src = reinterpret_cast<const uint4*>(p.B) + static_cast<size_t>(j) * kChunks + first_chunk;
+            // rows of the slice are ld halves apart; this block's columns start at column_block * N
+            const half* b_src = p.B + static_cast<size_t>(j) * kTileCols * p.ld + static_cast<size_t>(blockIdx.y) * N;
 #pragma unroll
             for (int i = 0; i < kChunks / (WPT * 32); i++) {
                 const uint32_t c   = first_chunk + i * WPT * 32;
                 const uint32_t row = c / kChunksPerRow, col = c % kChunksPerRow;
-                ptx::cp_async_16(dst + BT::swizzle(row * BT::kRowBytes + col * 16u), b_src + i * WPT * 32);
+                ptx::cp_async_16(dst + BT::swizzle(row * BT::kRowBytes + col * 16u),
+                                 b_src + static_cast<size_t>(row) * p.ld + col * 8);
             }
         };
         auto zero_a = [&]() {
@@ -508,14 +512,16 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     g_first--;
                 while (p.sched.chunk_begin[g_last + 1] < (row_tile + 1) * tiles_k)
                     g_last++;
-                float* mine = p.slots + (static_cast<size_t>(cta + above) * kTileRows + row_in_tile) * N;
+                float* const slots = p.slots + static_cast<size_t>(blockIdx.y) * p.slots_per_block_column * (kTileRows * N);
+                float* mine = slots + (static_cast<size_t>(cta + above) * kTileRows + row_in_tile) * N;
 #pragma unroll
                 for (int c = 0; c < N / 4; c++)
                     __stcg(reinterpret_cast<float4*>(mine) + c, make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]));
                 __threadfence();
                 __syncwarp();
                 unsigned int arrived = 0;
-                unsigned int* counter = &g_row_arrivals[row_tile * kEpilogueWarps + warp];
+                unsigned int* counter =
+                    &g_row_arrivals[(blockIdx.y * (p.m / kTileRows) + row_tile) * kEpilogueWarps + warp];
                 if (lane == 0)
                     arrived = atomicAdd(counter, 1u);
                 arrived = __shfl_sync(0xffffffffu, arrived, 0);
@@ -536,7 +542,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         }
                         else {
                             const float4* theirs = reinterpret_cast<const float4*>(
-                                p.slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N);
+                                slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N);
 #pragma unroll
                             for (int c = 0; c < N / 4; c++) {
                                 const float4 x = __ldcg(theirs + c);
@@ -560,7 +566,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     dst[static_cast<size_t>(n) * p.m] = __float2half_rn(acc[n]);
             }
             else if (write_c) {
-                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * N);
+                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
+                                                      + static_cast<size_t>(blockIdx.y) * N);
 #pragma unroll
                 for (int c = 0; c < N / 8; c++) {
                     __half2 h0 = __floats2half2_rn(acc[8 * c], acc[8 * c + 1]);
