@@ -12,6 +12,7 @@ from .spmm_api import (  # noqa: F401
     decompose,
     device_status,
     plan,
+    selftest_wait_timeout,
     spmm_own_scratch,
     synth_fp16,
     workspace_bytes,

@@ -79,7 +79,8 @@ __device__ __forceinline__ bool mbar_try_wait_suspend(uint32_t bar, uint32_t par
 constexpr uint64_t kWaitLimitNs = 2000000000ull;  // 2 s
 constexpr uint32_t kSuspendNs   = 20000u;
 
-__device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word)
+__device__ __forceinline__ bool
+mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word, uint64_t limit_ns = kWaitLimitNs)
 {
 #ifndef SPMM_B200_PLAIN_POLLS
 #define SPMM_B200_PLAIN_POLLS 64
@@ -100,7 +101,7 @@ __device__ __forceinline__ bool mbar_wait_bounded(uint32_t bar, uint32_t parity,
             const uint64_t now = global_timer_ns();
             if (start == 0)
                 start = now;
-            else if (now - start > kWaitLimitNs) {
+            else if (now - start > limit_ns) {
                 *abort_word = 1;
                 return false;
             }

@@ -488,6 +488,35 @@ int spmm_b200_device_status(int reset)
     return status;
 }
 
+namespace spmm_b200 {
+// One warp waits on a barrier that nothing ever arrives on: the bounded wait must give up after
+// limit_ns, record the event in the status word and let the block exit normally.
+__global__ void wait_that_runs_out_kernel(unsigned long long limit_ns)
+{
+    __shared__ __align__(8) uint64_t bar;
+    __shared__ int                   abort_word;
+    if (threadIdx.x == 0) {
+        ptx::mbar_init(ptx::smem_addr(&bar), 1);
+        ptx::mbar_init_fence();
+        abort_word = 0;
+    }
+    __syncthreads();
+    const bool ok = ptx::mbar_wait_bounded(ptx::smem_addr(&bar), 0, &abort_word, limit_ns);
+    __syncthreads();
+    if (threadIdx.x == 0 && !ok)
+        atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
+}
+}  // namespace spmm_b200
+
+int spmm_b200_selftest_wait_timeout(void* stream, unsigned int limit_ms)
+{
+    if (limit_ms == 0 || limit_ms > 1000)
+        return static_cast<int>(cudaErrorInvalidValue);
+    spmm_b200::wait_that_runs_out_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(
+        static_cast<unsigned long long>(limit_ms) * 1000000ull);
+    return static_cast<int>(cudaGetLastError());
+}
+
 int spmm_b200_plan(int tiles_m, int tiles_k, int max_ctas, long slots_avail, int* chunk_begin, int* split_rows_above,
                    int* slots_used)
 {

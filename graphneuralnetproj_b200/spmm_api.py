@@ -53,6 +53,8 @@ def _load():
         f.restype = None
     lib.spmm_b200_device_status.argtypes = [ctypes.c_int]
     lib.spmm_b200_device_status.restype = ctypes.c_int
+    lib.spmm_b200_selftest_wait_timeout.argtypes = [ctypes.c_void_p, ctypes.c_uint]
+    lib.spmm_b200_selftest_wait_timeout.restype = ctypes.c_int
     lib.spmm_b200_synth_fp16.argtypes = [_u16p, ctypes.c_long, ctypes.c_uint64, ctypes.c_double, ctypes.c_double]
     lib.spmm_b200_synth_fp16.restype = None
     lib.spmm_b200_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_long, _i32p, _i32p, _i32p]
@@ -183,6 +185,12 @@ def GenSparseMatrixBinFile(dense_path, M, K, nz_path, offsets_path, sizes_path):
 def device_status(reset=False):
     """0 if no kernel on the current device ever abandoned a wait; synchronises the device."""
     return int(LIB.spmm_b200_device_status(1 if reset else 0))
+
+
+def selftest_wait_timeout(limit_ms=50):
+    """Launches a wait that nothing satisfies; device_status() must report 1 afterwards (then reset it)."""
+    import torch
+    return int(LIB.spmm_b200_selftest_wait_timeout(ctypes.c_void_p(torch.cuda.current_stream().cuda_stream), limit_ms))
 
 
 def synth_fp16(shape, seed, sigma, p_zero=0.0):

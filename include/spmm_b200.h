@@ -103,6 +103,11 @@ void spmm_b200_decompose_v1(const uint16_t* A, uint16_t* A1, uint16_t* A2, int l
  * whose kernels cannot report anything. */
 int spmm_b200_device_status(int reset);
 
+/* Failure-detection self test: launches one warp that waits on a barrier nothing arrives on, with a
+ * limit of limit_ms (1..1000) milliseconds.  The bounded wait gives up, the kernel exits normally and
+ * spmm_b200_device_status() then reports 1 until it is reset.  No counterpart in the reference. */
+int spmm_b200_selftest_wait_timeout(void* stream, unsigned int limit_ms);
+
 /* Seeded synthetic inputs (stand-ins for pruned model weights and
  * activations): element i of the stream is drawn from a counter-based
  * splitmix64 generator, value = fp16(sigma * gaussian), zeroed with

@@ -202,3 +202,21 @@ def test_wide_n_in_column_blocks(sp, oracle, torch_cuda, case):
     block = run_spmm(sp, torch_cuda, words, offsets, np.ascontiguousarray(B[:, 64:128]), M, 64, K, 4)
     a, b = C[:, 64:128].view(np.float16).astype(np.float64), block.view(np.float16).astype(np.float64)
     assert np.abs(a - b).max() <= 2e-3 * np.abs(b).max()
+
+
+def test_a_wait_that_runs_out_is_reported_not_hung(sp, oracle, torch_cuda):
+    """Failure detection without a fault: a kernel waits on a barrier nothing arrives on; the bounded
+    wait gives up after 50 ms, the kernel returns, the status word says so, and the device keeps working."""
+    torch = torch_cuda
+    assert sp.device_status(reset=True) == 0
+    assert sp.selftest_wait_timeout(50) == 0
+    torch.cuda.synchronize()
+    assert sp.device_status() == 1
+    assert sp.device_status(reset=True) == 1
+    assert sp.device_status() == 0
+    M, K, N = 256, 256, 16
+    A = sp.synth_fp16((M, K), 91, 0.02, 0.8)
+    B = sp.synth_fp16((K, N), 92, 1.0, 0.0)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    C = run_spmm(sp, torch, words, offsets, B, M, N, K, 4)
+    assert oracle.tolerance_check(C, oracle.spmm_f64(A, B))[0]
