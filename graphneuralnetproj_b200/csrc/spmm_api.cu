@@ -19,10 +19,11 @@ namespace {
 // 4-word vectors held per lane; WPT * VPL * 32 vectors (7168 bytes of words) are in flight per slot.
 template<int N>
 struct DecodeConfig {
-    static constexpr int D   = N <= 32 ? 8 : 6;
-    static constexpr int Q   = N <= 32 ? 4 : 3;  // MMA-issuing warps
-    static constexpr int WPT = 1;
-    static constexpr int VPL = 14;
+    static constexpr int D    = 8;
+    static constexpr int Q    = 4;  // MMA-issuing warps
+    static constexpr int WPT  = 1;
+    static constexpr int VPL  = 14;
+    static constexpr int BBUF = N <= 32 ? 2 : 1;  // B buffers per ring slot: two do not fit at N = 64
 };
 
 struct DeviceInfo {
@@ -134,8 +135,8 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     constexpr int NB   = N < 16 ? 16 : N;
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
-    constexpr int smem = decode_smem_bytes<NB, D>();
-    auto          kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, 0, TM>;
+    constexpr int smem = decode_smem_bytes<NB, D, Cfg::BBUF>();
+    auto          kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, 0, TM, Cfg::BBUF>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {

@@ -109,10 +109,10 @@ struct BTile {
     }
 };
 
-template<int NB, int D>
+template<int NB, int D, int BBUF = 2>
 constexpr int decode_smem_bytes()
 {
-    return 1024 + D * (kATileBytes + 2 * BTile<NB>::kBytes) + 512;  // per ring slot: one A buffer, two B buffers
+    return 1024 + D * (kATileBytes + BBUF * BTile<NB>::kBytes) + 512;  // per ring slot: one A buffer, BBUF B buffers
 }
 
 template<int D, int Q, int WPT>
@@ -151,7 +151,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // TM : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
 //      library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
 //      k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TURNS = 0, int TM = 0>
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TURNS = 0, int TM = 0, int BBUF = 2>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
@@ -161,7 +161,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base    = smem_base;
     const uint32_t b_base    = a_base + D * kATileBytes;
-    const uint32_t bar_base  = b_base + 2 * D * BT::kBytes;
+    const uint32_t bar_base  = b_base + BBUF * D * BT::kBytes;
     // barrier map (8 bytes each): [0,D) tile full, [D,2D) tile free, then acc full x2, acc free x2
     auto tile_full = [&](int s) { return bar_base + 8u * s; };
     auto tile_free = [&](int s) { return bar_base + 8u * (D + s); };
@@ -205,7 +205,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     }
     // Clear the ring once: A buffers are kept all-zero between tiles, and columns N..NB-1 of the
     // staged B slices (N == 8) are never written.
-    for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(D * (kATileBytes + 2 * BT::kBytes));
+    for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(D * (kATileBytes + BBUF * BT::kBytes));
          off += blockDim.x * 16u)
         ptx::st_shared_zero_128(a_base + off);
     if (warp == kFirstMmaWarp) {
@@ -239,7 +239,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         auto stage_b = [&](int j, int parity) {
             if (ABL & 16)
                 return;
-            const uint32_t dst = b_base + (parity * D + s_own) * BT::kBytes;
+            const uint32_t dst = b_base + ((BBUF == 2 ? parity : 0) * D + s_own) * BT::kBytes;
             if (TM) {
                 // row n of the slice: 64 halves of token n starting at column 64 j (eight 16-byte chunks);
                 // chunk q of row n lands at n * 128 + ((q ^ (n % 8)) * 16)
@@ -350,8 +350,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             int j_next = j + D;
             while (j_next >= tiles_k)
                 j_next -= tiles_k;
-            if (has_next)
-                stage_b(j_next, (use + 1) & 1);
+            // With a single B buffer per slot, this tile's own slice is fetched now instead.
+            if (BBUF == 2 ? has_next : use > 0)
+                stage_b(BBUF == 2 ? j_next : j, (use + 1) & 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
             SPMM_FINE(fine, 2);
             if (!(ABL & 2)) {
@@ -388,7 +389,10 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 }
             }
             SPMM_FINE(fine, 4);
-            asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's B slice has landed
+            if (BBUF == 2)
+                asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's B slice has landed
+            else
+                asm volatile("cp.async.wait_group 0;" ::: "memory");
             SPMM_FINE(fine, 5);
             ptx::fence_proxy_async_smem();
             __syncwarp();
@@ -434,7 +438,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         break;
                     ptx::tc_fence_after_sync();
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kATileBytes >> 4));
-                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((parity * D + s) * (BT::kBytes >> 4));
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((BBUF == 2 ? parity : 0) * D + s) * (BT::kBytes >> 4));
 #pragma unroll
                     for (int k = 0; k < ((ABL & 8) ? 0 : kTileCols / 16); k++) {
                         // A: 16 k values = 32 bytes along the swizzled row; B: 16 k rows = two 8-row groups.
@@ -471,38 +475,63 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             if (!warp_wait(acc_full(seg & 1), (seg >> 1) & 1, abort_word, lane))
                 break;
             ptx::tc_fence_after_sync();
-            // Add the accumulators of the MMA warps that issued for this segment, in warp order.
-            float acc[N];
+            // The segment's result is handled in chunks of CH columns to keep registers low: the sum, in
+            // warp order, of the accumulators of the MMA warps that issued for this segment.
+            constexpr int CH = N < 16 ? 8 : 16;
+            auto load_chunk = [&](int c, float* out) {
 #pragma unroll
-            for (int n = 0; n < N; n++)
-                acc[n] = 0.0f;
+                for (int n = 0; n < CH; n++)
+                    out[n] = 0.0f;
 #pragma unroll
-            for (int q = 0; q < Q; q++) {
-                if (((q - l) % Q + Q) % Q < len) {
-                    float          part[N];
-                    const uint32_t taddr = tmem_base + ((seg & 1) * Q + q) * NB + (static_cast<uint32_t>(warp * 32) << 16);
-                    if (N == 8) {
-                        ptx::tmem_ld_x8(taddr, reinterpret_cast<uint32_t*>(part));
+                for (int q = 0; q < Q; q++) {
+                    if (((q - l) % Q + Q) % Q < len) {
+                        float          part[CH];
+                        const uint32_t taddr =
+                            tmem_base + ((seg & 1) * Q + q) * NB + c * CH + (static_cast<uint32_t>(warp * 32) << 16);
+                        if (CH == 8)
+                            ptx::tmem_ld_x8(taddr, reinterpret_cast<uint32_t*>(part));
+                        else
+                            ptx::tmem_ld_x16(taddr, reinterpret_cast<uint32_t*>(part));
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int n = 0; n < CH; n++)
+                            out[n] += part[n];
                     }
-                    else {
+                }
+            };
+            auto store_c_chunk = [&](int c, const float* v) {
+                if (TM) {
+                    half* dst = p.C + static_cast<size_t>(row_tile) * kTileRows + row_in_tile;  // C[n][m]
 #pragma unroll
-                        for (int c = 0; c < N / 16; c++)
-                            ptx::tmem_ld_x16(taddr + c * 16, reinterpret_cast<uint32_t*>(part) + c * 16);
-                    }
-                    ptx::tmem_ld_wait();
+                    for (int n = 0; n < CH; n++)
+                        dst[static_cast<size_t>(c * CH + n) * p.m] = __float2half_rn(v[n]);
+                    return;
+                }
+                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
+                                                      + static_cast<size_t>(blockIdx.y) * N + c * CH);
 #pragma unroll
-                    for (int n = 0; n < N; n++)
-                        acc[n] += part[n];
+                for (int i = 0; i < CH / 8; i++) {
+                    __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]);
+                    __half2 h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
+                    __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
+                    __half2 h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                    uint4   o;
+                    o.x    = *reinterpret_cast<uint32_t*>(&h0);
+                    o.y    = *reinterpret_cast<uint32_t*>(&h1);
+                    o.z    = *reinterpret_cast<uint32_t*>(&h2);
+                    o.w    = *reinterpret_cast<uint32_t*>(&h3);
+                    dst[i] = o;
+                }
+            };
+            if (whole) {
+#pragma unroll 1
+                for (int c = 0; c < N / CH; c++) {
+                    float v[CH];
+                    load_chunk(c, v);
+                    store_c_chunk(c, v);
                 }
             }
-            ptx::tmem_ld_wait();
-            ptx::tc_fence_before_sync();
-            __syncwarp();
-            if (lane == 0)
-                ptx::mbar_arrive(acc_free(seg & 1));
-
-            bool write_c = whole;
-            if (!whole) {
+            else {
                 // Park the partial row, count arrivals, let the last arriver sum in owner order.
                 const int  head_row  = tile_begin / tiles_k;
                 const bool head_part = (tile_begin % tiles_k != 0) || (tile_end < (head_row + 1) * tiles_k);
@@ -513,13 +542,19 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 while (p.sched.chunk_begin[g_last + 1] < (row_tile + 1) * tiles_k)
                     g_last++;
                 float* const slots = p.slots + static_cast<size_t>(blockIdx.y) * p.slots_per_block_column * (kTileRows * N);
-                float* mine = slots + (static_cast<size_t>(cta + above) * kTileRows + row_in_tile) * N;
+                float*       mine  = slots + (static_cast<size_t>(cta + above) * kTileRows + row_in_tile) * N;
+#pragma unroll 1
+                for (int c = 0; c < N / CH; c++) {
+                    float v[CH];
+                    load_chunk(c, v);
 #pragma unroll
-                for (int c = 0; c < N / 4; c++)
-                    __stcg(reinterpret_cast<float4*>(mine) + c, make_float4(acc[4 * c], acc[4 * c + 1], acc[4 * c + 2], acc[4 * c + 3]));
+                    for (int i = 0; i < CH / 4; i++)
+                        __stcg(reinterpret_cast<float4*>(mine + c * CH) + i,
+                               make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                }
                 __threadfence();
                 __syncwarp();
-                unsigned int arrived = 0;
+                unsigned int  arrived = 0;
                 unsigned int* counter =
                     &g_row_arrivals[(blockIdx.y * (p.m / kTileRows) + row_tile) * kEpilogueWarps + warp];
                 if (lane == 0)
@@ -529,59 +564,43 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     if (lane == 0)
                         *counter = 0;
                     __threadfence();
-                    float sum[N];
-#pragma unroll
-                    for (int n = 0; n < N; n++)
-                        sum[n] = 0.0f;
 #pragma unroll 1
-                    for (int g = g_first; g <= g_last; g++) {
-                        if (g == cta) {
+                    for (int c = 0; c < N / CH; c++) {
+                        float own[CH], sum[CH];
+                        load_chunk(c, own);  // the accumulators are still held: read them again
 #pragma unroll
-                            for (int n = 0; n < N; n++)
-                                sum[n] += acc[n];
-                        }
-                        else {
-                            const float4* theirs = reinterpret_cast<const float4*>(
-                                slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N);
+                        for (int n = 0; n < CH; n++)
+                            sum[n] = 0.0f;
+#pragma unroll 1
+                        for (int g = g_first; g <= g_last; g++) {
+                            if (g == cta) {
 #pragma unroll
-                            for (int c = 0; c < N / 4; c++) {
-                                const float4 x = __ldcg(theirs + c);
-                                sum[4 * c] += x.x;
-                                sum[4 * c + 1] += x.y;
-                                sum[4 * c + 2] += x.z;
-                                sum[4 * c + 3] += x.w;
+                                for (int n = 0; n < CH; n++)
+                                    sum[n] += own[n];
+                            }
+                            else {
+                                const float4* theirs = reinterpret_cast<const float4*>(
+                                    slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N + c * CH);
+#pragma unroll
+                                for (int i = 0; i < CH / 4; i++) {
+                                    const float4 x = __ldcg(theirs + i);
+                                    sum[4 * i] += x.x;
+                                    sum[4 * i + 1] += x.y;
+                                    sum[4 * i + 2] += x.z;
+                                    sum[4 * i + 3] += x.w;
+                                }
                             }
                         }
+                        store_c_chunk(c, sum);
                     }
-#pragma unroll
-                    for (int n = 0; n < N; n++)
-                        acc[n] = sum[n];
-                    write_c = true;
                 }
             }
-            if (write_c && TM) {
-                half* dst = p.C + static_cast<size_t>(row_tile) * kTileRows + row_in_tile;  // C[n][m]
-#pragma unroll
-                for (int n = 0; n < N; n++)
-                    dst[static_cast<size_t>(n) * p.m] = __float2half_rn(acc[n]);
-            }
-            else if (write_c) {
-                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
-                                                      + static_cast<size_t>(blockIdx.y) * N);
-#pragma unroll
-                for (int c = 0; c < N / 8; c++) {
-                    __half2 h0 = __floats2half2_rn(acc[8 * c], acc[8 * c + 1]);
-                    __half2 h1 = __floats2half2_rn(acc[8 * c + 2], acc[8 * c + 3]);
-                    __half2 h2 = __floats2half2_rn(acc[8 * c + 4], acc[8 * c + 5]);
-                    __half2 h3 = __floats2half2_rn(acc[8 * c + 6], acc[8 * c + 7]);
-                    uint4   o;
-                    o.x    = *reinterpret_cast<uint32_t*>(&h0);
-                    o.y    = *reinterpret_cast<uint32_t*>(&h1);
-                    o.z    = *reinterpret_cast<uint32_t*>(&h2);
-                    o.w    = *reinterpret_cast<uint32_t*>(&h3);
-                    dst[c] = o;
-                }
-            }
+            // only now may the MMA warps overwrite this accumulator set
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive(acc_free(seg & 1));
             l += len;
         }
     }
