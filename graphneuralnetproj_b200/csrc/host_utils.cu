@@ -1,12 +1,15 @@
 // Host-side helpers behind include/spmm_b200.h: the 2:4 + residual split of
 // kernel_benchmark/spmm_decompose.h:12-142 and the seeded input generator.
+#include <cassert>
 #include <cmath>
+#include <cstdio>
 #include <cstdint>
 #include <cstring>
 
 #include <cuda_fp16.h>
 
 #include "../../include/spmm_b200.h"
+#include "../../include/spmm_decompose.h"
 #include "host_threads.h"
 
 namespace {
@@ -63,6 +66,41 @@ inline double unit_open(uint64_t x)
 }
 
 }  // namespace
+
+// C++ entry points with the names and signatures of kernel_benchmark/spmm_decompose.h:12 and :53,
+// declared in include/spmm_decompose.h.  Like the reference they report how the nonzeros were split.
+namespace {
+void report_split(const half* A1, const half* A2, int length)
+{
+    long nnz1 = 0, nnz2 = 0;
+    const uint16_t* a1 = reinterpret_cast<const uint16_t*>(A1);
+    const uint16_t* a2 = reinterpret_cast<const uint16_t*>(A2);
+    for (long i = 0; i < length; i++) {
+        nnz1 += splits_as_nonzero(a1[i]);
+        nnz2 += splits_as_nonzero(a2[i]);
+    }
+    const double total = static_cast<double>(nnz1 + nnz2);
+    printf("NNZ1= %ld ratio = %f pad_nnz=%d \nNNZ2= %ld ratio = %f\n", nnz1, total > 0 ? nnz1 / total : 0.0, length * 2 / 4,
+           nnz2, total > 0 ? nnz2 / total : 0.0);
+    printf("A1 padding ratio = %f\n", 1 - nnz1 * 1.0 / (length * 2 / 4));
+}
+}  // namespace
+
+void decompose(half* A, half* A1, half* A2, int length)
+{
+    assert(length % 4 == 0);
+    split_groups(reinterpret_cast<const uint16_t*>(A), reinterpret_cast<uint16_t*>(A1), reinterpret_cast<uint16_t*>(A2),
+                 length, false);
+    report_split(A1, A2, length);
+}
+
+void decompose_v1(half* A, half* A1, half* A2, int length)
+{
+    assert(length % 4 == 0);
+    split_groups(reinterpret_cast<const uint16_t*>(A), reinterpret_cast<uint16_t*>(A1), reinterpret_cast<uint16_t*>(A2),
+                 length, true);
+    report_split(A1, A2, length);
+}
 
 extern "C" {
 

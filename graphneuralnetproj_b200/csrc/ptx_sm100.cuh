@@ -109,6 +109,20 @@ mbar_wait_bounded(uint32_t bar, uint32_t parity, volatile int* abort_word, uint6
     }
 }
 
+// Waits, for at most limit_ns, without looking at the abort word: used on the way out of an
+// abandoned block to let a bulk copy that is still in flight land before the block exits.
+__device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, uint64_t limit_ns)
+{
+    const uint64_t start = global_timer_ns();
+#pragma unroll 1
+    for (;;) {
+        if (mbar_try_wait_suspend(bar, parity, kSuspendNs))
+            return true;
+        if (global_timer_ns() - start > limit_ns)
+            return false;
+    }
+}
+
 // ---------------------------------------------------------------- copies
 // 16-byte asynchronous copy, bypassing L1.
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src)
@@ -136,6 +150,13 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes)
 {
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ uint4 ld_shared_128(uint32_t addr)
+{
+    uint4 v;
+    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
+    return v;
 }
 
 // Streaming 128-bit load of read-only data that is used exactly once.

@@ -19,11 +19,13 @@ namespace {
 // 4-word vectors held per lane; WPT * VPL * 32 vectors (7168 bytes of words) are in flight per slot.
 template<int N>
 struct DecodeConfig {
-    static constexpr int D    = 8;
+    static constexpr int D    = 8;  // decoder warps
     static constexpr int Q    = 4;  // MMA-issuing warps
     static constexpr int WPT  = 1;
     static constexpr int VPL  = 14;
-    static constexpr int BBUF = N <= 32 ? 2 : 1;  // B buffers per ring slot: two do not fit at N = 64
+    static constexpr int S    = 8;                 // ring slots
+    static constexpr int BBUF = 1;                 // B buffers per ring slot
+    static constexpr int WTMA = N <= 32 ? 1 : 0;   // words staged through shared memory by bulk copy
 };
 
 struct DeviceInfo {
@@ -70,41 +72,29 @@ const Schedule& cached_schedule(const PlanKey& key)
 }
 
 #ifdef SPMM_B200_ABLATIONS
-template<int D, int Q, int WPT, int ABL>
+// Experiment builds only: ring shapes and ablation masks chosen through the environment (N = 16).
+template<int D, int Q, int S, int BBUF, int WTMA, int ABL>
 cudaError_t launch_ablated(cudaStream_t stream, const DecodeParams& params)
 {
-    constexpr int smem = decode_smem_bytes<16, D>();
-    const char* envt = getenv("SPMM_B200_TURNS");
-    const int turns = envt ? atoi(envt) : 0;
-    auto kern = turns == 1 ? spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, 1>
-              : turns == 2 ? spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, (D % 2 == 0 ? 2 : 0)>
-              : turns == 4 ? spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, (D > 4 && D % 4 == 0 ? 4 : 0)>
-                           : spmm_decode_kernel<16, D, Q, WPT, 14 / WPT, ABL, 0>;
+    constexpr int smem = decode_smem_bytes<16, S, BBUF, WTMA ? word_stage_bytes<D, 1, 14>() : 0>();
+    const char*   envp = getenv("SPMM_B200_PFR");
+    const int     pfr  = envp ? atoi(envp) : 2;
+    auto          kern = pfr == 4 ? spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 4>
+                       : pfr == 8 ? spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 8>
+                       : pfr == 1 ? spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 1>
+                                  : spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 2>;
     cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    kern<<<params.sched.num_ctas, decode_threads<D, Q, WPT>(), smem, stream>>>(params);
+    if (const char* envs = getenv("SPMM_B200_CARVEOUT"))
+        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, atoi(envs));
+    kern<<<params.sched.num_ctas, decode_threads<D, Q, 1>(), smem, stream>>>(params);
     return cudaGetLastError();
 }
-template<int D, int Q, int WPT>
+template<int D, int Q, int S, int BBUF, int WTMA>
 cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, int abl)
 {
     switch (abl) {
-        case 1: return launch_ablated<D, Q, WPT, 1>(stream, params);
-        case 2: return launch_ablated<D, Q, WPT, 2>(stream, params);
-        case 3: return launch_ablated<D, Q, WPT, 3>(stream, params);
-        case 4: return launch_ablated<D, Q, WPT, 4>(stream, params);
-        case 12: return launch_ablated<D, Q, WPT, 12>(stream, params);
-        case 13: return launch_ablated<D, Q, WPT, 13>(stream, params);
-        case 28: return launch_ablated<D, Q, WPT, 28>(stream, params);
-        case 29: return launch_ablated<D, Q, WPT, 29>(stream, params);
-        case 30: return launch_ablated<D, Q, WPT, 30>(stream, params);
-        case 14: return launch_ablated<D, Q, WPT, 14>(stream, params);
-        case 15: return launch_ablated<D, Q, WPT, 15>(stream, params);
-        case 9: return launch_ablated<D, Q, WPT, 9>(stream, params);
-        case 10: return launch_ablated<D, Q, WPT, 10>(stream, params);
-        case 8: return launch_ablated<D, Q, WPT, 8>(stream, params);
-        case 11: return launch_ablated<D, Q, WPT, 11>(stream, params);
-        case 31: return launch_ablated<D, Q, WPT, 31>(stream, params);
-        default: return launch_ablated<D, Q, WPT, 0>(stream, params);
+        case 3: return launch_ablated<D, Q, S, BBUF, WTMA, 3>(stream, params);
+        default: return launch_ablated<D, Q, S, BBUF, WTMA, 0>(stream, params);
     }
 }
 #endif
@@ -115,28 +105,23 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
 {
 #ifdef SPMM_B200_ABLATIONS
     if (N == 16 && !TM) {
-        const char* env = getenv("SPMM_B200_ABLATE");
-        const char* envd = getenv("SPMM_B200_D");
-        const int abl = env ? atoi(env) : 0;
-        switch (envd ? atoi(envd) : 842) {   // D * 100 + Q * 10 + WPT
-            case 841: return launch_ablated_d<8, 4, 1>(stream, params, abl);
-            case 441: return launch_ablated_d<4, 4, 1>(stream, params, abl);
-            case 1021: return launch_ablated_d<10, 2, 1>(stream, params, abl);
-            case 821: return launch_ablated_d<8, 2, 1>(stream, params, abl);
-            case 822: return launch_ablated_d<8, 2, 2>(stream, params, abl);
-            case 1022: return launch_ablated_d<10, 2, 2>(stream, params, abl);
-            case 1052: return launch_ablated_d<10, 5, 2>(stream, params, abl);
-            case 932: return launch_ablated_d<9, 3, 2>(stream, params, abl);
-            case 812: return launch_ablated_d<8, 1, 2>(stream, params, abl);
-            default: return launch_ablated_d<8, 4, 2>(stream, params, abl);
+        const char* env  = getenv("SPMM_B200_ABLATE");
+        const char* envc = getenv("SPMM_B200_CFG");
+        const int   abl  = env ? atoi(env) : 0;
+        switch (envc ? atoi(envc) : 0) {
+            case 1: return launch_ablated_d<8, 4, 8, 2, 0>(stream, params, abl);
+            case 3: return launch_ablated_d<8, 4, 8, 1, 1>(stream, params, abl);
+            default: break;
         }
     }
 #endif
     constexpr int NB   = N < 16 ? 16 : N;
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
-    constexpr int smem = decode_smem_bytes<NB, D, Cfg::BBUF>();
-    auto          kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, 0, TM, Cfg::BBUF>;
+    constexpr int smem =
+        decode_smem_bytes<NB, Cfg::S, Cfg::BBUF, Cfg::WTMA ? word_stage_bytes<D, Cfg::WPT, Cfg::VPL>() : 0>();
+    static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
+    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, TM, Cfg::BBUF, Cfg::S, Cfg::WTMA>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -203,7 +188,8 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.m            = M_Global;
     params.ld           = N_Global;
     // with several column blocks the blocks of one column share the SMs with the other columns
-    params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots});
+    params.sched = cached_schedule(PlanKey{
+        tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots});
     params.slots_per_block_column = params.sched.slots_used;
     if (wide)
         return launch_decode<64>(stream, dev, 3, params, column_blocks);

@@ -109,10 +109,19 @@ struct BTile {
     }
 };
 
-template<int NB, int D, int BBUF = 2>
+// Per ring slot one A buffer and BBUF B buffers; STAGE bytes of word staging buffers (0 when the
+// words are loaded straight into registers).
+template<int NB, int S, int BBUF = 2, int STAGE = 0>
 constexpr int decode_smem_bytes()
 {
-    return 1024 + D * (kATileBytes + BBUF * BTile<NB>::kBytes) + 512;  // per ring slot: one A buffer, BBUF B buffers
+    return 1024 + S * (kATileBytes + BBUF * BTile<NB>::kBytes) + STAGE + 512;
+}
+
+// Staging bytes for D decoder teams that each hold WPT * VPL * 32 vectors of 16 bytes.
+template<int D, int WPT, int VPL>
+constexpr int word_stage_bytes()
+{
+    return D * WPT * VPL * 32 * 16;
 }
 
 template<int D, int Q, int WPT>
@@ -140,35 +149,44 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 }
 
 // N   : columns of B / C (8, 16, 32, 64);   NB : columns of the staged B tile (16 when N == 8)
-// D   : depth of the tile ring;  Q : MMA-issuing warps;  WPT : decoder warps per ring slot;
+// D   : decoder teams;  Q : MMA-issuing warps;  WPT : decoder warps per team;
 // VPL : 4-word vectors held per lane
+// S   : slots of the tile ring (0 = D).  Tile l of the chunk is decoded by team l % D into slot l % S
+//       and multiplied by MMA warp l % Q.  With S > D a team moves on to a slot whose previous MMA
+//       was issued S - D tiles earlier, instead of waiting out the round trip of its own last tile.
+// WTMA : 1 = a tile's words travel global -> shared memory by bulk copy (one staging buffer per
+//       team, completion on an mbarrier) and are then read into registers, instead of being loaded
+//       into registers directly.  Register loads are tracked in L1, whose size (what the shared
+//       memory carve-out leaves) then bounds the bytes in flight; the copy engine has no such bound.
+// PFR : a team asks for the words of its tile PFR rounds ahead (tile l + PFR * D) to be brought into L2.
+// BBUF : B buffers per slot.  2: the next tile's slice is fetched while this one is decoded (needs
+//       S == D); 1: the slice is fetched after the slot has been handed back.
 // ABL : debugging ablation mask (0 in production): 1 no clearing, 2 no scatter, 4 no word loads,
 //       8 no MMA, 16 no B copy
-// TURNS : at most this many ring slots are cleared and scattered at the same time (0 = no limit).
-//         Decoders that share the load/store unit evenly all finish together and then all wait for
-//         their MMAs together, so the store phase and the MMA round trip add up instead of
-//         overlapping; taking turns keeps the hand-overs staggered.
 // TM : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
 //      library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
 //      k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TURNS = 0, int TM = 0, int BBUF = 2>
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TM = 0, int BBUF = 2, int S_ = 0, int WTMA = 0, int PFR = 2>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
     constexpr int NB = N < 16 ? 16 : N;
+    constexpr int S  = S_ == 0 ? D : S_;
     using BT         = BTile<NB>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base    = smem_base;
-    const uint32_t b_base    = a_base + D * kATileBytes;
-    const uint32_t bar_base  = b_base + BBUF * D * BT::kBytes;
-    // barrier map (8 bytes each): [0,D) tile full, [D,2D) tile free, then acc full x2, acc free x2
+    const uint32_t b_base    = a_base + S * kATileBytes;
+    const uint32_t w_base    = b_base + BBUF * S * BT::kBytes;  // word staging, one buffer per team
+    constexpr int  kStageBytes = WPT * VPL * 32 * 16;
+    const uint32_t bar_base  = w_base + (WTMA ? D * kStageBytes : 0);
+    // barrier map (8 bytes each): [0,S) tile full, [S,2S) tile free, then acc full x2, acc free x2
     auto tile_full = [&](int s) { return bar_base + 8u * s; };
-    auto tile_free = [&](int s) { return bar_base + 8u * (D + s); };
-    auto acc_full  = [&](int b) { return bar_base + 8u * (2 * D + b); };
-    auto acc_free  = [&](int b) { return bar_base + 8u * (2 * D + 2 + b); };
-    auto turn = [&](int s) { return bar_base + 8u * (2 * D + 4 + s); };
-    const uint32_t tmem_slot_addr = bar_base + 8u * (3 * D + 4);
+    auto tile_free = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full  = [&](int b) { return bar_base + 8u * (2 * S + b); };
+    auto acc_free  = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
+    auto words_full = [&](int t) { return bar_base + 8u * (2 * S + 4 + t); };
+    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4 + D);
     uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
     volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
@@ -184,28 +202,28 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     constexpr int      kFirstDecodeWarp = kFirstMmaWarp + Q;
     constexpr uint32_t kTmemCols        = tmem_columns(2 * Q * NB);  // accumulator (q, b) at column (b * Q + q) * NB
     static_assert(2 * Q * NB <= 512, "accumulators exceed the 512 TMEM columns");
-    static_assert(D % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
-    static_assert(TURNS < D && (TURNS == 0 || D % TURNS == 0),
-                  "TURNS must divide D: the next arrival on a turn barrier must depend on its current waiter");
+    static_assert(S % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
+    static_assert(S >= D && S < 2 * D + 1, "a team must find its registers' tile a slot no later than one lap ahead");
+    static_assert(BBUF == 1 || S == D, "fetching the next B slice early needs a slot that stays with its team");
+    static_assert(8 * (2 * S + 4 + D) + 8 <= 512, "barrier block");
 
     if (threadIdx.x == 0) {
-        for (int s = 0; s < D; s++) {
+        for (int s = 0; s < S; s++) {
             ptx::mbar_init(tile_full(s), WPT);
             ptx::mbar_init(tile_free(s), 1);
         }
+        for (int t = 0; t < D; t++)
+            ptx::mbar_init(words_full(t), 1);
         for (int b = 0; b < 2; b++) {
             ptx::mbar_init(acc_full(b), Q);
             ptx::mbar_init(acc_free(b), kEpilogueWarps);
-        }
-        for (int s = 0; s < D; s++) {
-            ptx::mbar_init(turn(s), WPT);
         }
         *abort_word = 0;
         ptx::mbar_init_fence();
     }
     // Clear the ring once: A buffers are kept all-zero between tiles, and columns N..NB-1 of the
     // staged B slices (N == 8) are never written.
-    for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(D * (kATileBytes + BBUF * BT::kBytes));
+    for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(S * (kATileBytes + BBUF * BT::kBytes));
          off += blockDim.x * 16u)
         ptx::st_shared_zero_128(a_base + off);
     if (warp == kFirstMmaWarp) {
@@ -221,9 +239,10 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 
     if (warp >= kFirstDecodeWarp) {
         // ------------------------------------------------------------ decoder team
-        const int      s_own  = (warp - kFirstDecodeWarp) / WPT;  // ring slot of this team
-        const int      h      = (warp - kFirstDecodeWarp) % WPT;  // this warp's share of the tile
-        const uint32_t a_tile = a_base + s_own * kATileBytes;
+        const int s_own = (warp - kFirstDecodeWarp) / WPT;  // this team; also its first tile and first slot
+        const int h     = (warp - kFirstDecodeWarp) % WPT;  // this warp's share of the tile
+        uint32_t  slot  = s_own;                            // ring slot of the tile being decoded
+        uint32_t  a_tile = a_base + slot * kATileBytes;
         auto team_sync = [&]() {
             if (WPT > 1)
                 asm volatile("bar.sync %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
@@ -239,7 +258,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         auto stage_b = [&](int j, int parity) {
             if (ABL & 16)
                 return;
-            const uint32_t dst = b_base + ((BBUF == 2 ? parity : 0) * D + s_own) * BT::kBytes;
+            const uint32_t dst = b_base + ((BBUF == 2 ? parity : 0) * S + slot) * BT::kBytes;
             if (TM) {
                 // row n of the slice: 64 halves of token n starting at column 64 j (eight 16-byte chunks);
                 // chunk q of row n lands at n * 128 + ((q ^ (n % 8)) * 16)
@@ -283,11 +302,42 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         r[v] = ptx::ld_stream_128(from + v * WPT * 32);
                 }
         };
+        // WTMA: the first VPL * WPT * 32 vectors of a tile come through the team's staging buffer.
+        const uint32_t stage   = w_base + s_own * kStageBytes;
+        bool           pending = false;  // a bulk copy into the staging buffer has not been waited for
+        uint32_t       wphase  = 0;      // completed waits on this team's words_full barrier
+        auto fetch_words = [&](const uint4* from, int count) {
+            pending = true;
+            if (h == 0 && lane == 0) {
+                const uint32_t bytes = static_cast<uint32_t>(min(count, VPL * WPT * 32)) * 16u;
+                if (bytes > 0 && !(ABL & 4)) {
+                    ptx::mbar_arrive_expect_tx(words_full(s_own), bytes);
+                    ptx::bulk_copy_g2s(stage, from, bytes, words_full(s_own));
+                }
+                else
+                    ptx::mbar_arrive(words_full(s_own));
+            }
+        };
+        auto take_words = [&](int count) {
+            uint32_t seen = 0;
+#pragma unroll
+            for (int v = 0; v < VPL; v++)
+                if (lane_vec + v * WPT * 32 < count) {
+                    if (ABL & 4)
+                        r[v] = make_uint4(lane << 17, (lane + 32) << 17, (lane + 64) << 17, (lane + 96) << 17);
+                    else
+                        r[v] = ptx::ld_shared_128(stage + static_cast<uint32_t>(lane_vec + v * WPT * 32) * 16u);
+                    seen ^= r[v].w;
+                }
+            // a use of every loaded register: the loads have returned before the buffer is handed
+            // back to the copy engine
+            asm volatile("" ::"r"(seen) : "memory");
+        };
         const uint4* src = p.words + lane_vec;  // always offset by this lane's first vector
         // Offsets are read two tiles ahead (next*: tile l + D, after*: tile l + 2D) so that the words of
         // tile l + 2D can be requested into L2 while tile l is being decoded; the register loads of
         // tile l + D, issued after this tile's scatter, then find their lines in L2.
-        int  after0 = 0, after1 = 0;
+        int  after0 = 0, after1 = 0, pf0 = 0, pf1 = 0;
         auto prefetch_tile = [&](int off0, int off1) {
             if (h == 0 && lane == 0 && off1 > off0)
                 ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
@@ -297,8 +347,12 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const int off1 = __ldg(p.tile_offsets + tile_begin + s_own + 1);
             nvec           = off1 - off0;
             src            = p.words + off0 + lane_vec;
-            load_words(src, nvec);
-            stage_b(j, 0);
+            if (WTMA)
+                fetch_words(p.words + off0, nvec);
+            else
+                load_words(src, nvec);
+            if (BBUF == 2)
+                stage_b(j, 0);
             if (s_own + D < num_tiles) {
                 next0 = __ldg(p.tile_offsets + tile_begin + s_own + D);
                 next1 = __ldg(p.tile_offsets + tile_begin + s_own + D + 1);
@@ -309,38 +363,49 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 after1 = __ldg(p.tile_offsets + tile_begin + s_own + 2 * D + 1);
                 prefetch_tile(after0, after1);
             }
+#pragma unroll 1
+            for (int k = 3; k <= PFR; k++)
+                if (s_own + k * D < num_tiles)
+                    prefetch_tile(__ldg(p.tile_offsets + tile_begin + s_own + k * D),
+                                  __ldg(p.tile_offsets + tile_begin + s_own + k * D + 1));
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (s_own == 0 && h == 0)
             SPMM_TRACE(1);  // first loads issued
-        int use = 0;
+        int use = 0;  // tiles this team has decoded
 #pragma unroll 1
         for (int l = s_own; l < num_tiles; l += D, ++use) {
             const bool has_next = l + D < num_tiles;
             const bool fine     = (s_own == 0 && h == 0 && use == 8);
+            const int  lap      = l / S;  // how often this slot has been filled before
             SPMM_FINE(fine, 0);
-            if (use > 0 && l + 2 * D < num_tiles)
-                prefetch_tile(after0, after1);  // offsets were requested one iteration ago
-            if (use > 0) {
-                if (!ptx::mbar_wait_bounded(tile_free(s_own), (use - 1) & 1, abort_word)) {
+            SPMM_FINE(s_own == 0 && h == 0 && use == 9, 10);
+            if (use > 0)
+                prefetch_tile(pf0, pf1);  // tile l + PFR * D; its offsets were requested one iteration ago
+            if (WTMA) {
+                // this tile's words: staging buffer -> registers, then the buffer takes the next tile
+                if (!ptx::mbar_wait_bounded(words_full(s_own), wphase & 1, abort_word)) {
+                    if (WPT > 1)
+                        asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
+                    break;
+                }
+                pending = false;
+                ++wphase;
+                SPMM_FINE(fine, 8);
+                take_words(nvec);
+                team_sync();
+                if (has_next)
+                    fetch_words(p.words + next0, next1 - next0);
+                SPMM_FINE(fine, 9);
+            }
+            if (lap > 0) {
+                if (!ptx::mbar_wait_bounded(tile_free(slot), (lap - 1) & 1, abort_word)) {
                     // A team mate that saw the barrier complete may be waiting at the team barrier below.
                     if (WPT > 1)
                         asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
                     break;
                 }
                 SPMM_FINE(fine, 7);
-            }
-            if (TURNS > 0 && l >= TURNS) {
-                // wait until tile l - TURNS has been scattered: the decoder of slot (l - TURNS) % D arrives
-                // on this slot's turn barrier; slots below TURNS get no arrival for their first tile
-                const uint32_t phase = s_own < TURNS ? (use - 1) : use;
-                if (!ptx::mbar_wait_bounded(turn(s_own), phase & 1, abort_word)) {
-                    if (WPT > 1)
-                        asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
-                    break;
-                }
-            }
-            if (use > 0) {
                 if (!(ABL & 1))
                     zero_a();
                 team_sync();  // the whole buffer is clear before anyone scatters into it
@@ -351,7 +416,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             while (j_next >= tiles_k)
                 j_next -= tiles_k;
             // With a single B buffer per slot, this tile's own slice is fetched now instead.
-            if (BBUF == 2 ? has_next : use > 0)
+            if (BBUF == 2 ? has_next : true)
                 stage_b(BBUF == 2 ? j_next : j, (use + 1) & 1);
             asm volatile("cp.async.commit_group;" ::: "memory");
             SPMM_FINE(fine, 2);
@@ -371,22 +436,23 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     if (lane_vec + v * WPT * 32 < nvec - done)
                         ptx::scatter_words(a_tile, r[v]);
             }
-            if (TURNS > 0) {
-                __syncwarp();
-                if (lane == 0)
-                    ptx::mbar_arrive(turn((s_own + TURNS) % D));  // tile l + TURNS may start its stores
-            }
             SPMM_FINE(fine, 3);
             if (has_next) {
                 nvec = next1 - next0;
                 src  = p.words + next0 + lane_vec;
-                load_words(src, nvec);
+                if (!WTMA)
+                    load_words(src, nvec);
                 next0 = after0;
                 next1 = after1;
                 if (l + 3 * D < num_tiles) {
                     after0 = __ldg(p.tile_offsets + tile_begin + l + 3 * D);
                     after1 = __ldg(p.tile_offsets + tile_begin + l + 3 * D + 1);
                 }
+            }
+            pf0 = pf1 = 0;
+            if (l + (PFR + 1) * D < num_tiles) {
+                pf0 = __ldg(p.tile_offsets + tile_begin + l + (PFR + 1) * D);
+                pf1 = __ldg(p.tile_offsets + tile_begin + l + (PFR + 1) * D + 1);
             }
             SPMM_FINE(fine, 4);
             if (BBUF == 2)
@@ -397,11 +463,17 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0)
-                ptx::mbar_arrive(tile_full(s_own));
+                ptx::mbar_arrive(tile_full(slot));
             SPMM_FINE(fine, 6);
             j = j_next;
+            slot += D;
+            if (slot >= S)
+                slot -= S;
+            a_tile = a_base + slot * kATileBytes;
         }
         ptx::cp_async_wait_all();
+        if (WTMA && pending)  // only on the way out of an abandoned block
+            ptx::mbar_wait_quiet(words_full(s_own), wphase & 1, 1000000ull);
         if (s_own == 0 && h == 0)
             SPMM_TRACE(6);
     }
@@ -431,14 +503,14 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 uint32_t accumulate = 0;
 #pragma unroll 1
                 for (int l = first; l < l0 + len && ok; l += Q) {
-                    const int      s      = l % D;
-                    const uint32_t parity = (l / D) & 1;
+                    const int      s      = l % S;
+                    const uint32_t parity = (l / S) & 1;
                     ok = ptx::mbar_wait_bounded(tile_full(s), parity, abort_word);
                     if (!ok)
                         break;
                     ptx::tc_fence_after_sync();
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kATileBytes >> 4));
-                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((BBUF == 2 ? parity : 0) * D + s) * (BT::kBytes >> 4));
+                    const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((BBUF == 2 ? parity : 0) * S + s) * (BT::kBytes >> 4));
 #pragma unroll
                     for (int k = 0; k < ((ABL & 8) ? 0 : kTileCols / 16); k++) {
                         // A: 16 k values = 32 bytes along the swizzled row; B: 16 k rows = two 8-row groups.

@@ -88,6 +88,21 @@ def test_decompose_matches_oracle(sp, oracle):
         assert np.array_equal(a1, b1) and np.array_equal(a2, b2)
 
 
+def test_decompose_cxx_entry_points(sp):
+    """decompose / decompose_v1 with the reference's C++ signatures (include/spmm_decompose.h) agree with the C ABI."""
+    import ctypes
+    A = sp.synth_fp16((128, 256), 19, 0.02, 0.55)
+    for v1, symbol in ((False, "_Z9decomposeP6__halfS0_S0_i"), (True, "_Z12decompose_v1P6__halfS0_S0_i")):
+        fn = getattr(sp.spmm_api.LIB, symbol)
+        fn.restype = None
+        fn.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_void_p, ctypes.c_int]
+        a1 = np.full(A.shape, 0xFFFF, np.uint16)
+        a2 = np.full(A.shape, 0xFFFF, np.uint16)
+        fn(A.ctypes.data, a1.ctypes.data, a2.ctypes.data, A.size)
+        b1, b2 = sp.decompose(A, v1=v1)
+        assert np.array_equal(a1, b1) and np.array_equal(a2, b2)
+
+
 def test_gen_sparse_matrix_bin_file(sp, tmp_path):
     M, K = 256, 128
     A = sp.synth_fp16((M, K), 23, 0.02, 0.8)
