@@ -365,7 +365,7 @@ def run_sweep(args):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
     peak, _ = measured_hbm_peak()
-    shapes = [(n, m, k) for n, m, k, _ in LAYERS]
+    shapes = [(n, m, k) for n, m, k, _ in LAYERS if n in args.sweep_layers.split(",")]
     n_list = [int(x) for x in args.sweep_n.split(",")]
     p_list = [float(x) for x in args.sweep_p.split(",")]
     for name, M, K in shapes:
@@ -484,6 +484,7 @@ def main():
     ap.add_argument("--sweep", action="store_true", help="decode-size sweep (layers x N x sparsity) instead of the bench line")
     ap.add_argument("--sweep-n", default="8,16,32,64")
     ap.add_argument("--sweep-p", default="0.7,0.8,0.9")
+    ap.add_argument("--sweep-layers", default="qkv,out_proj,ffn1,ffn2")
     ap.add_argument("--prefill", action="store_true", help="prefill-size points (N >= 256) instead of the bench line")
     ap.add_argument("--prefill-n", default="256,512,1024,2048")
     ap.add_argument("--small", action="store_true", help="with --prefill: only the 12288 x 12288 shape")

@@ -254,6 +254,32 @@ umma_f16_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, u
                  : "memory");
 }
 
+// D[tmem] (+)= A[smem] * B[smem] with A stored 2:4-compressed (two of every four k values) and
+// the selector metadata of the 128 x 32 logical A operand in TMEM.  `e_tmem` is the even column of a
+// pair; the instruction descriptor carries the sparse flag and, in its two lowest bits, which column
+// of the pair to use (make_idesc_f16_f32(...) | kIdescSparse | column & 1).
+__device__ __forceinline__ void
+umma_f16_sp_ss(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t e_tmem, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %5, 0;\n\t"
+                 "tcgen05.mma.sp.cta_group::1.kind::f16 [%0], %1, %2, [%3], %4, {%6, %6, %6, %6}, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc),
+                 "l"(b_desc),
+                 "r"(e_tmem),
+                 "r"(idesc),
+                 "r"(accumulate),
+                 "r"(0u)
+                 : "memory");
+}
+
+// Copies 128 rows x 16 bytes from shared memory (described by a matrix descriptor) to TMEM lanes
+// 0..127, four 32-bit columns starting at `taddr`.  Ordered with the MMAs the same thread issues.
+__device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t smem_desc)
+{
+    asm volatile("tcgen05.cp.cta_group::1.128x128b [%0], %1;" ::"r"(taddr), "l"(smem_desc) : "memory");
+}
+
 // Arrives on the mbarrier once every UMMA issued so far by this thread has completed.
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
@@ -319,6 +345,8 @@ __host__ __device__ constexpr uint32_t make_idesc_f16_f32(int m, int n, bool a_m
            | (static_cast<uint32_t>(a_mn_major) << 15) | (static_cast<uint32_t>(b_mn_major) << 16)
            | (static_cast<uint32_t>(n >> 3) << 17) | (static_cast<uint32_t>(m >> 4) << 24);
 }
+
+constexpr uint32_t kIdescSparse = 1u << 2;  // A is 2:4-compressed, metadata in TMEM
 
 }  // namespace ptx
 }  // namespace spmm_b200

@@ -11,6 +11,7 @@
 #include "../../include/spmm_b200.h"
 #include "host_threads.h"
 #include "spmm_decode_kernel.cuh"
+#include "spmm_structured_kernel.cuh"
 
 namespace spmm_b200 {
 namespace {
@@ -30,7 +31,7 @@ struct DecodeConfig {
 
 struct DeviceInfo {
     int  sm_count = 0;
-    bool attrs_set[8] = {false, false, false, false, false, false, false, false};
+    bool attrs_set[12] = {};  // cudaFuncSetAttribute done, per kernel instantiation
 };
 
 DeviceInfo& device_info(int device)
@@ -147,7 +148,8 @@ namespace {
 
 // Shared by both layouts: validates, partitions, launches.  token_major: B[N][K], C[N][M].
 cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const int* TileOffsets, const half* B, half* C,
-                           int M_Global, int N_Global, int K_Global, half* Reduction_Workspace, int Split_K, bool token_major)
+                           int M_Global, int N_Global, int K_Global, half* Reduction_Workspace, int Split_K, bool token_major,
+                           const float* addend = nullptr, size_t workspace_skip_bytes = 0)
 {
     // N: 8, 16, 32, 64 as in the reference (csrc/SpMM_API.cu:105-196); multiples of 64 beyond that are
     // served by the same kernel, one 64-column block per blockIdx.y (row-major layout only).
@@ -173,16 +175,19 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
 
     const int  tiles_m = M_Global / kTileRows, tiles_k = K_Global / kTileCols;
     // every column block gets an equal share of the workspace for its partial tiles
-    const long slots   = Reduction_Workspace
-                             ? static_cast<long>(static_cast<size_t>(Split_K) * M_Global * N_Global * sizeof(half)
-                                                 / (static_cast<size_t>(kTileRows) * n_block * sizeof(float)) / column_blocks)
-                             : 0;
+    // (a caller that keeps the head of the workspace for itself passes its size as workspace_skip_bytes)
+    const size_t workspace_bytes = static_cast<size_t>(Split_K) * M_Global * N_Global * sizeof(half);
+    const long   slots           = Reduction_Workspace && workspace_bytes > workspace_skip_bytes
+                                       ? static_cast<long>((workspace_bytes - workspace_skip_bytes)
+                                                           / (static_cast<size_t>(kTileRows) * n_block * sizeof(float)) / column_blocks)
+                                       : 0;
     DecodeParams params;
     params.words        = Compressed_A;
     params.tile_offsets = TileOffsets;
     params.B            = B;
     params.C            = C;
-    params.slots        = reinterpret_cast<float*>(Reduction_Workspace);
+    params.slots        = reinterpret_cast<float*>(reinterpret_cast<char*>(Reduction_Workspace) + workspace_skip_bytes);
+    params.addend       = addend;
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
     params.m            = M_Global;
@@ -217,6 +222,92 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     }
 }
 
+template<int N, int STAGES>
+cudaError_t launch_structured(cudaStream_t stream, DeviceInfo& dev, int n_index, const StructuredParams& params)
+{
+    constexpr int NB   = N < 16 ? 16 : N;
+    constexpr int smem = structured_smem_bytes<NB, STAGES>();
+    static_assert(smem <= 227 * 1024, "stages do not fit in shared memory");
+    auto kern = spmm_structured_kernel<N, STAGES>;
+    if (!dev.attrs_set[n_index]) {
+        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (e != cudaSuccess) {
+            (void)cudaGetLastError();
+            return e;
+        }
+        dev.attrs_set[n_index] = true;
+    }
+    kern<<<params.sched.num_ctas, kStructuredThreads, smem, stream>>>(params);
+    return cudaGetLastError();
+}
+
+// Heterogeneous product C = A1 * B + A2 * B: A1 (at most two nonzeros per aligned group of four along
+// K) packed by InitSparseMatrixA1_tcgen05, A2 as tiled-CSL or absent.  With a residual the structured
+// kernel leaves its product in fp32 at the head of the workspace and the tiled-CSL kernel adds it
+// before the single rounding to fp16.
+cudaError_t spmm_hetero(cudaStream_t stream, const half* values, const int* metadata, const uint4* residual_words,
+                        const int* residual_offsets, const half* B, half* C, int M_Global, int N_Global, int K_Global,
+                        half* Reduction_Workspace, int Split_K)
+{
+    if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
+        printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
+        return cudaErrorUnknown;
+    }
+    if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kBlockK != 0
+        || M_Global / kTileRows > kMaxRowTiles || Split_K < 1)
+        return cudaErrorInvalidValue;
+    if (!values || !metadata || !B || !C || !aligned16(values) || !aligned16(metadata) || !aligned16(B) || !aligned16(C)
+        || !aligned16(Reduction_Workspace))
+        return cudaErrorInvalidValue;
+    const bool   residual      = residual_words != nullptr && residual_offsets != nullptr;
+    const size_t partial_bytes = static_cast<size_t>(M_Global) * N_Global * sizeof(float);
+    const size_t workspace     = Reduction_Workspace ? static_cast<size_t>(Split_K) * M_Global * N_Global * sizeof(half) : 0;
+    if (residual && workspace < partial_bytes)
+        return cudaErrorInvalidValue;  // the fp32 hand-over needs Split_K >= 2 worth of workspace
+
+    int         device = 0;
+    cudaError_t e      = cudaGetDevice(&device);
+    if (e != cudaSuccess)
+        return e;
+    DeviceInfo& dev = device_info(device);
+
+    const size_t skip    = residual ? partial_bytes : 0;
+    const int    tiles_m = M_Global / kTileRows, blocks_k = K_Global / kBlockK;
+    const long   slots   = workspace > skip
+                               ? static_cast<long>((workspace - skip) / (static_cast<size_t>(kTileRows) * N_Global * sizeof(float)))
+                               : 0;
+    StructuredParams params;
+    params.values   = reinterpret_cast<const uint4*>(values);
+    params.meta     = reinterpret_cast<const uint4*>(metadata);
+    params.B        = B;
+    params.C        = C;
+    params.C32      = residual ? reinterpret_cast<float*>(Reduction_Workspace) : nullptr;
+    params.slots    = reinterpret_cast<float*>(reinterpret_cast<char*>(Reduction_Workspace) + skip);
+    params.n        = N_Global;
+    params.blocks_k = blocks_k;
+    params.m        = M_Global;
+    params.ld       = N_Global;
+    params.sched    = cached_schedule(PlanKey{tiles_m, blocks_k, dev.sm_count, slots});
+    switch (N_Global) {
+        case 8:
+            e = launch_structured<8, 9>(stream, dev, 8, params);
+            break;
+        case 16:
+            e = launch_structured<16, 9>(stream, dev, 9, params);
+            break;
+        case 32:
+            e = launch_structured<32, 8>(stream, dev, 10, params);
+            break;
+        default:
+            e = launch_structured<64, 6>(stream, dev, 11, params);
+            break;
+    }
+    if (e != cudaSuccess || !residual)
+        return e;
+    return spmm_tiled_csl(stream, residual_words, residual_offsets, B, C, M_Global, N_Global, K_Global, Reduction_Workspace,
+                          Split_K, false, params.C32, skip);
+}
+
 }  // namespace
 }  // namespace spmm_b200
 
@@ -234,15 +325,10 @@ cudaError_t SpMM_SplitK_API(cudaStream_t    stream,
                             half*           Reduction_Workspace,
                             int             Split_K)
 {
-    (void)A;
     (void)A1_Ind_data;
-    if (metadata != nullptr) {
-        if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
-            printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
-            return cudaErrorUnknown;
-        }
-        return cudaErrorNotSupported;  // structured (2:4) half: not handled by this kernel
-    }
+    if (metadata != nullptr)  // heterogeneous mode: A and metadata from InitSparseMatrixA1_tcgen05
+        return spmm_b200::spmm_hetero(stream, A, metadata, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,
+                                      Reduction_Workspace, Split_K);
     return spmm_b200::spmm_tiled_csl(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,
                                      Reduction_Workspace, Split_K, false);
 }

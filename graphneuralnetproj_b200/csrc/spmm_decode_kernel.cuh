@@ -91,6 +91,7 @@ struct DecodeParams {
     int          m;             // M
     int          ld;            // row stride of B[K][ld] and C[M][ld] in halves (row-major layout): the full N
     int          slots_per_block_column;  // workspace slots used by one column block (blockIdx.y)
+    const float* addend;        // optional fp32 [M][N] added before the rounding (row-major results, N <= 64 only)
     Schedule     sched;
 };
 
@@ -581,6 +582,24 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 }
                 uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
                                                       + static_cast<size_t>(blockIdx.y) * N + c * CH);
+                float w[CH];
+#pragma unroll
+                for (int n = 0; n < CH; n++)
+                    w[n] = v[n];
+                if (p.addend != nullptr) {
+                    // the product of the structured half of the same matrix, left in fp32 by its kernel
+                    const float4* add = reinterpret_cast<const float4*>(
+                        p.addend + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * N + c * CH);
+#pragma unroll
+                    for (int i = 0; i < CH / 4; i++) {
+                        const float4 x = __ldcg(add + i);
+                        w[4 * i] += x.x;
+                        w[4 * i + 1] += x.y;
+                        w[4 * i + 2] += x.z;
+                        w[4 * i + 3] += x.w;
+                    }
+                }
+                v = w;
 #pragma unroll
                 for (int i = 0; i < CH / 8; i++) {
                     __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]);

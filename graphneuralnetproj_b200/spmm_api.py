@@ -45,6 +45,9 @@ def _load():
     lib.spmm_b200_spmm_own_scratch.restype = ctypes.c_int
     lib.spmm_b200_spmm_splitk_token_major.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
     lib.spmm_b200_spmm_splitk_token_major.restype = ctypes.c_int
+    lib.spmm_b200_pack_a1.argtypes = [_u16p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
+                                      ctypes.POINTER(ctypes.c_void_p)]
+    lib.spmm_b200_pack_a1.restype = ctypes.c_int
     lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
     for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):
@@ -175,6 +178,29 @@ def decompose(A, v1=False):
     fn = LIB.spmm_b200_decompose_v1 if v1 else LIB.spmm_b200_decompose
     fn(flat.ctypes.data_as(_u16p), A1.ctypes.data_as(_u16p), A2.ctypes.data_as(_u16p), flat.size)
     return A1.reshape(A.shape), A2.reshape(A.shape)
+
+
+def InitSparseMatrixA1_tcgen05(A1_h, M, K):
+    """Packs the structured half A1[M][K] (at most two nonzeros per aligned group of four along K, as
+    `decompose` returns it) for the heterogeneous mode of SpMM_SplitK_API.
+
+    Returns (values, metadata, blocks): uint8 array of 16 KB per 128 x 128 block (argument A of
+    SpMM_SplitK_API once on the device) and uint32 array of 2 KB per block (argument metadata).
+    Raises ValueError on a violated precondition."""
+    A1_h = _host_u16(A1_h)
+    if A1_h.size != M * K:
+        raise ValueError("A1 must hold M * K halves")
+    values, meta = ctypes.c_void_p(), ctypes.c_void_p()
+    blocks = LIB.spmm_b200_pack_a1(A1_h.ctypes.data_as(_u16p), M, K, ctypes.byref(values), ctypes.byref(meta))
+    if blocks < 0:
+        raise ValueError("M and K must be multiples of 128 and A1 must hold at most two nonzeros per group of four")
+    try:
+        v = np.ctypeslib.as_array(ctypes.cast(values, ctypes.POINTER(ctypes.c_uint8)), shape=(blocks * 16384,)).copy()
+        m = np.ctypeslib.as_array(ctypes.cast(meta, ctypes.POINTER(ctypes.c_uint32)), shape=(blocks * 512,)).copy()
+    finally:
+        LIB.spmm_b200_free(values)
+        LIB.spmm_b200_free(meta)
+    return v, m, blocks
 
 
 def GenSparseMatrixBinFile(dense_path, M, K, nz_path, offsets_path, sizes_path):

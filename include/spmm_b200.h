@@ -95,6 +95,16 @@ size_t spmm_b200_workspace_bytes(int M_Global, int N_Global, int Split_K);
  * split A into a 2:4-compliant part A1 and the residual A2 (both dense, length
  * elements, caller-allocated). */
 void spmm_b200_decompose(const uint16_t* A, uint16_t* A1, uint16_t* A2, int length);
+
+/* Packs the structured half A1[M][K] (host, fp16 bits, at most two nonzeros in every aligned group
+ * of four along K, e.g. the A1 that decompose returns) for the heterogeneous mode of
+ * spmm_b200_spmm_splitk: *values (16 KB per 128 x 128 block) is passed as its argument A,
+ * *metadata (2 KB per block) as its argument metadata, both copied to the device by the caller.
+ * M and K multiples of 128.  Both arrays are malloc'd here and owned by the caller (free()).
+ * Returns the number of blocks, or -1 (nothing allocated) if a shape or the 2:4 condition is
+ * violated.  Takes the place of the reference's InitSparseMatrixA1_Vec_Sparse_Load +
+ * inspect_metadata pair (csrc/SpMM_API.cu:1127-1553), whose formats serve its Ampere kernel. */
+int spmm_b200_pack_a1(const uint16_t* A1, int M, int K, void** values, void** metadata);
 void spmm_b200_decompose_v1(const uint16_t* A, uint16_t* A1, uint16_t* A2, int length);
 
 /* Device-side status of the current device: 0 = ok, 1 = a bounded wait inside a
