@@ -474,6 +474,107 @@ def run_prefill(args):
     assert sp.device_status() == 0
 
 
+def prune_2_of_4(A_bits, keep_prob, seed):
+    """2:4 magnitude pruning along K, then each survivor is zeroed with probability 1 - keep_prob."""
+    groups = np.abs(A_bits.view(np.float16).astype(np.float32)).reshape(-1, 4)
+    order = np.argsort(-groups, axis=1, kind="stable")
+    mask = np.zeros(groups.shape, dtype=bool)
+    np.put_along_axis(mask, order[:, :2], True, axis=1)
+    mask &= np.random.default_rng(seed).random(mask.shape) < keep_prob
+    out = A_bits.reshape(-1, 4).copy()
+    out[~mask] = 0
+    return out.reshape(A_bits.shape)
+
+
+def run_hetero(args):
+    """Heterogeneous decomposition (M = K = 12288, N = 32): the structured half on tcgen05.mma.sp plus the
+    tiled-CSL residual, against the same matrix encoded wholly as tiled-CSL and against cuBLAS dense.
+    Two inputs: 2:4 magnitude pruning with half of the survivors zeroed (75 % sparse, empty residual) and
+    i.i.d. 80 % sparsity (a few per cent of the nonzeros land in the residual).  One JSON line each."""
+    import torch
+
+    import graphneuralnetproj_b200 as sp
+    dev = torch.device("cuda:0")
+    torch.cuda.set_device(0)
+    peak, _ = measured_hbm_peak()
+    M = K = args.hetero_size
+    N = 32
+
+    def timed(fn, copies):
+        for i in range(3):
+            fn(i)
+        torch.cuda.synchronize()
+        stream = torch.cuda.Stream()
+        with torch.cuda.stream(stream):
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph, stream=stream):
+                for i in range(2 * copies):
+                    fn(i)
+            graph.replay()
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            reps = 10
+            e0.record(stream)
+            for _ in range(reps):
+                graph.replay()
+            e1.record(stream)
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1000.0 / (reps * 2 * copies)
+
+    Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB400, 1.0).view(np.int16)).to(dev)
+    Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
+    ws = torch.zeros(sp.workspace_bytes(M, N, 8) // 2, dtype=torch.int16, device=dev)
+    copies = 2  # rotate over two copies of the weights: more than L2 holds
+    for label, make in (("2:4 pruned, half of the survivors zeroed (75 % sparse)",
+                         lambda: prune_2_of_4(sp.synth_fp16((M, K), 0xA400, 0.02, 0.0), 0.5, 4)),
+                        ("i.i.d. 80 % sparse", lambda: sp.synth_fp16((M, K), 0xA401, 0.02, 0.8))):
+        A = make()
+        A1, A2 = sp.decompose(A)
+        residual_nnz = int(np.count_nonzero(A2 & 0x7FFF))
+        values, meta, _ = sp.InitSparseMatrixA1_tcgen05(A1, M, K)
+        vds = [torch.from_numpy(values).to(dev) for _ in range(copies)]
+        mds = [torch.from_numpy(meta.view(np.int32)).to(dev) for _ in range(copies)]
+        a1_bytes = values.nbytes + meta.nbytes
+        r_wds = r_od = None
+        residual_bytes = 0
+        if residual_nnz:
+            rw, ro, rn = sp.InitSparseMatrixA_API(A2, M, N, K)
+            r_wds = [torch.from_numpy(np.concatenate([rw, np.zeros(4, np.uint32)]).view(np.int32)).to(dev) for _ in range(copies)]
+            r_od = torch.from_numpy(ro).to(dev)
+            residual_bytes = 4 * rw.size + 4 * rn
+        words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, N, K)
+        wds = [torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev) for _ in range(copies)]
+        od = torch.from_numpy(offsets).to(dev)
+        csl_bytes = 4 * words.size + 4 * n_offsets
+        Ad = [torch.from_numpy(A.view(np.float16)).to(dev) for _ in range(copies)]
+        Bh = Bd.view(torch.float16)
+
+        def hetero(i):
+            rc = sp.SpMM_SplitK_API(None, vds[i % copies], r_wds[i % copies] if r_wds else None, None, mds[i % copies],
+                                    r_od, Bd, Cd, M, N, K, ws, 8)
+            assert rc == 0, rc
+
+        def csl(i):
+            rc = sp.SpMM_SplitK_API(None, None, wds[i % copies], None, None, od, Bd, Cd, M, N, K, ws, 8)
+            assert rc == 0, rc
+
+        t_hetero = timed(hetero, copies)
+        t_csl = timed(csl, copies)
+        t_dense = timed(lambda i: torch.matmul(Ad[i % copies], Bh), copies)
+        algo = a1_bytes + residual_bytes + 2 * K * N + 2 * M * N
+        print(json.dumps({"input": label, "M": M, "K": K, "N": N, "residual_nnz": residual_nnz,
+                          "hetero_us": round(t_hetero, 2), "tiled_csl_only_us": round(t_csl, 2),
+                          "cublas_dense_us": round(t_dense, 2),
+                          "a1_bytes": a1_bytes, "residual_bytes": residual_bytes, "tiled_csl_bytes": csl_bytes,
+                          "hetero_weight_gbs": round((a1_bytes + residual_bytes) / t_hetero / 1e3, 1),
+                          "hetero_roofline_frac": round(algo / t_hetero / 1e3 / peak, 4),
+                          "tiled_csl_roofline_frac": round((csl_bytes + 2 * K * N + 2 * M * N) / t_csl / 1e3 / peak, 4),
+                          "speedup_vs_cublas": round(t_dense / t_hetero, 3)}), flush=True)
+        del vds, mds, wds, Ad, r_wds
+        torch.cuda.empty_cache()
+    assert sp.device_status() == 0
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -488,8 +589,12 @@ def main():
     ap.add_argument("--prefill", action="store_true", help="prefill-size points (N >= 256) instead of the bench line")
     ap.add_argument("--prefill-n", default="256,512,1024,2048")
     ap.add_argument("--small", action="store_true", help="with --prefill: only the 12288 x 12288 shape")
+    ap.add_argument("--hetero", action="store_true", help="heterogeneous decomposition points (structured half on the sparse tensor core)")
+    ap.add_argument("--hetero-size", type=int, default=12288)
     args = ap.parse_args()
-    if args.prefill:
+    if args.hetero:
+        run_hetero(args)
+    elif args.prefill:
         run_prefill(args)
     elif args.sweep:
         run_sweep(args)
