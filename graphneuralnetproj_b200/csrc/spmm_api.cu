@@ -16,22 +16,25 @@
 namespace spmm_b200 {
 namespace {
 
-// Ring depth D (bounded by 227 KB of shared memory per block), decoder warps per ring slot and
-// 4-word vectors held per lane; WPT * VPL * 32 vectors (7168 bytes of words) are in flight per slot.
+// Shape of the block per width of the B slice (bounded by 227 KB of shared memory and 512 TMEM
+// columns): D decoder teams of WPT warps, Q MMA-issuing warps, S ring slots, VPL 4-word vectors
+// held per lane (WPT * VPL * 32 vectors = 7168 bytes of words in flight per team).
+// Up to 64 columns the kernel is bound by decoding; 128 and 256 columns serve prefill sizes, where a
+// decoded tile feeds four 128 x N x 16 MMAs of 64-128 cycles each and fewer, wider slots are enough.
 template<int N>
 struct DecodeConfig {
-    static constexpr int D    = 8;  // decoder warps
-    static constexpr int Q    = 4;  // MMA-issuing warps
-    static constexpr int WPT  = 1;
-    static constexpr int VPL  = 14;
-    static constexpr int S    = 8;                 // ring slots
+    static constexpr int D    = N <= 64 ? 8 : 4;   // decoder teams
+    static constexpr int WPT  = N <= 64 ? 1 : 2;   // warps per team
+    static constexpr int Q    = N <= 64 ? 4 : (N == 128 ? 2 : 1);  // MMA-issuing warps (2 * Q * N TMEM columns)
+    static constexpr int VPL  = 14 / WPT;
+    static constexpr int S    = N <= 64 ? 8 : (N == 128 ? 6 : 4);  // ring slots
     static constexpr int BBUF = 1;                 // B buffers per ring slot
-    static constexpr int WTMA = N <= 32 ? 1 : 0;   // words staged through shared memory by bulk copy
+    static constexpr int WTMA = N == 64 ? 0 : 1;   // words staged through shared memory by bulk copy
 };
 
 struct DeviceInfo {
     int  sm_count = 0;
-    bool attrs_set[12] = {};  // cudaFuncSetAttribute done, per kernel instantiation
+    bool attrs_set[16] = {};  // cudaFuncSetAttribute done, per kernel instantiation
 };
 
 DeviceInfo& device_info(int device)
@@ -112,6 +115,10 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
         switch (envc ? atoi(envc) : 0) {
             case 1: return launch_ablated_d<8, 4, 8, 2, 0>(stream, params, abl);
             case 3: return launch_ablated_d<8, 4, 8, 1, 1>(stream, params, abl);
+            case 4: return launch_ablated_d<6, 3, 9, 1, 1>(stream, params, abl);
+            case 5: return launch_ablated_d<6, 2, 10, 1, 1>(stream, params, abl);
+            case 6: return launch_ablated_d<6, 4, 8, 1, 1>(stream, params, abl);
+            case 7: return launch_ablated_d<4, 2, 10, 1, 1>(stream, params, abl);
             default: break;
         }
     }
@@ -158,8 +165,9 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
         return cudaErrorUnknown;
     }
-    const int column_blocks = wide ? N_Global / 64 : 1;
-    const int n_block       = wide ? 64 : N_Global;
+    // the widest slice that divides N: the sparse tiles are decoded once per column block
+    const int n_block       = !wide ? N_Global : (N_Global % 256 == 0 ? 256 : (N_Global % 128 == 0 ? 128 : 64));
+    const int column_blocks = N_Global / n_block;
     if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kTileCols != 0
         || static_cast<long>(M_Global / kTileRows) * column_blocks > kMaxRowTiles || Split_K < 1)
         return cudaErrorInvalidValue;
@@ -196,8 +204,16 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.sched = cached_schedule(PlanKey{
         tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots});
     params.slots_per_block_column = params.sched.slots_used;
-    if (wide)
-        return launch_decode<64>(stream, dev, 3, params, column_blocks);
+    if (wide) {
+        switch (n_block) {
+            case 256:
+                return launch_decode<256>(stream, dev, 13, params, column_blocks);
+            case 128:
+                return launch_decode<128>(stream, dev, 12, params, column_blocks);
+            default:
+                return launch_decode<64>(stream, dev, 3, params, column_blocks);
+        }
+    }
     if (token_major) {
         switch (N_Global) {
             case 8:

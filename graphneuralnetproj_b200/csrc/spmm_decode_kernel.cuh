@@ -81,32 +81,45 @@ __device__ __forceinline__ long long fine_clock()
 #endif
 
 struct DecodeParams {
-    const uint4* words;         // tiled-CSL words, viewed as 4-word vectors
-    const int*   tile_offsets;  // vectors before each tile
-    const half*  B;             // [K][N] row-major
-    half*        C;             // [M][N] row-major
-    float*       slots;         // fp32 partial tiles, 128 * N floats each
-    int          n;             // N (8, 16, 32 or 64)
-    int          tiles_k;       // K / 64
-    int          m;             // M
-    int          ld;            // row stride of B[K][ld] and C[M][ld] in halves (row-major layout): the full N
-    int          slots_per_block_column;  // workspace slots used by one column block (blockIdx.y)
-    const float* addend;        // optional fp32 [M][N] added before the rounding (row-major results, N <= 64 only)
+    const uint4* words        = nullptr;  // tiled-CSL words, viewed as 4-word vectors
+    const int*   tile_offsets = nullptr;  // vectors before each tile
+    const half*  B            = nullptr;  // [K][N] row-major
+    half*        C            = nullptr;  // [M][N] row-major
+    float*       slots        = nullptr;  // fp32 partial tiles, 128 * N floats each
+    int          n            = 0;        // N (8, 16, 32 or 64)
+    int          tiles_k      = 0;        // K / 64
+    int          m            = 0;        // M
+    int          ld           = 0;  // row stride of B[K][ld] and C[M][ld] in halves (row-major layout): the full N
+    int          slots_per_block_column = 0;  // workspace slots used by one column block (blockIdx.y)
+    const float* addend = nullptr;  // optional fp32 [M][N] added before the rounding (row-major results, N <= 64 only)
     Schedule     sched;
 };
 
+// Staged 64 x NB slice of B[K][N] (N-contiguous, "MN-major" for the tensor core).  Up to 64 columns a
+// row of the slice is one swizzle row (32, 64 or 128 bytes); wider slices are cut into atoms of 64
+// columns, each a 64 x 128-byte block of its own (the descriptor's leading offset steps over atoms).
 template<int NB>
 struct BTile {
-    static constexpr int      kRowBytes    = NB * 2;
-    static constexpr int      kBytes       = kTileCols * kRowBytes;
-    static constexpr int      kSwizzleBits = NB == 16 ? 1 : (NB == 32 ? 2 : 3);
+    static constexpr int      kAtomCols    = NB > 64 ? 64 : NB;
+    static constexpr int      kAtoms       = NB / kAtomCols;
+    static constexpr int      kRowBytes    = kAtomCols * 2;
+    static constexpr int      kAtomBytes   = kTileCols * kRowBytes;
+    static constexpr int      kBytes       = kAtoms * kAtomBytes;
+    static constexpr int      kSwizzleBits = kAtomCols == 16 ? 1 : (kAtomCols == 32 ? 2 : 3);
     static constexpr uint64_t kSwizzleMode =
-        NB == 16 ? ptx::kSwizzle32B : (NB == 32 ? ptx::kSwizzle64B : ptx::kSwizzle128B);
-    static constexpr int kGroupBytes = 8 * kRowBytes;  // eight k rows: the descriptor's stride offset
+        kAtomCols == 16 ? ptx::kSwizzle32B : (kAtomCols == 32 ? ptx::kSwizzle64B : ptx::kSwizzle128B);
+    static constexpr int kGroupBytes   = 8 * kRowBytes;  // eight k rows: the descriptor's stride offset
+    static constexpr int kLeadingBytes = kAtoms > 1 ? kAtomBytes : kGroupBytes;  // the descriptor's leading offset
     // XOR the 16-byte chunk index with address bits 7.. (Swizzle<bits,4,3> on byte offsets).
     __device__ static __forceinline__ uint32_t swizzle(uint32_t byte_offset)
     {
         return byte_offset ^ (((byte_offset >> 7) & ((1u << kSwizzleBits) - 1u)) << 4);
+    }
+    // Byte offset of 16-byte chunk `chunk` (of the NB-wide row) of k row `row`.
+    __device__ static __forceinline__ uint32_t offset(uint32_t row, uint32_t chunk)
+    {
+        constexpr uint32_t kChunksPerAtomRow = kRowBytes / 16;
+        return (chunk / kChunksPerAtomRow) * kAtomBytes + swizzle(row * kRowBytes + (chunk % kChunksPerAtomRow) * 16u);
     }
 };
 
@@ -204,7 +217,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     constexpr uint32_t kTmemCols        = tmem_columns(2 * Q * NB);  // accumulator (q, b) at column (b * Q + q) * NB
     static_assert(2 * Q * NB <= 512, "accumulators exceed the 512 TMEM columns");
     static_assert(S % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
-    static_assert(S >= D && S < 2 * D + 1, "a team must find its registers' tile a slot no later than one lap ahead");
+    static_assert(S >= D, "every team needs a slot of its own to start with");
     static_assert(BBUF == 1 || S == D, "fetching the next B slice early needs a slot that stays with its team");
     static_assert(8 * (2 * S + 4 + D) + 8 <= 512, "barrier block");
 
@@ -279,7 +292,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             for (int i = 0; i < kChunks / (WPT * 32); i++) {
                 const uint32_t c   = first_chunk + i * WPT * 32;
                 const uint32_t row = c / kChunksPerRow, col = c % kChunksPerRow;
-                ptx::cp_async_16(dst + BT::swizzle(row * BT::kRowBytes + col * 16u),
+                ptx::cp_async_16(dst + BT::offset(row, col),
                                  b_src + static_cast<size_t>(row) * p.ld + col * 8);
             }
         };
@@ -394,6 +407,11 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 ++wphase;
                 SPMM_FINE(fine, 8);
                 take_words(nvec);
+                // With two warps per team the copy engine's next write into the staging buffer is
+                // issued by the other warp: this warp's reads are ordered before it by a proxy fence
+                // on this side of the team barrier (without it results were wrong on the GPU).
+                if (WPT > 1)
+                    ptx::fence_proxy_async_smem();
                 team_sync();
                 if (has_next)
                     fetch_words(p.words + next0, next1 - next0);
@@ -490,7 +508,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
             const uint64_t     b_desc0 =
                 TM ? ptx::make_smem_desc(b_base, 16, 1024, ptx::kSwizzle128B)
-                   : ptx::make_smem_desc(b_base, BT::kGroupBytes, BT::kGroupBytes, BT::kSwizzleMode);
+                   : ptx::make_smem_desc(b_base, BT::kLeadingBytes, BT::kGroupBytes, BT::kSwizzleMode);
             bool ok  = true;
             int  seg = 0;
 #pragma unroll 1

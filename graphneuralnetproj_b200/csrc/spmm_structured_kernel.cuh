@@ -49,16 +49,16 @@ constexpr int kBLoaderWarps      = 2;
 constexpr int kBLag              = 3;  // a B slice is announced this many blocks after its copies were issued
 
 struct StructuredParams {
-    const uint4* values;  // blocks * 16 KB
-    const uint4* meta;    // blocks * 2 KB
-    const half*  B;       // [K][ld]
-    half*        C;       // [M][ld] fp16 result, used when C32 == nullptr
-    float*       C32;     // [M][N] fp32 result for a following residual product, or nullptr
-    float*       slots;   // fp32 partial blocks of split rows
-    int          n;
-    int          blocks_k;  // K / 128
-    int          m;
-    int          ld;
+    const uint4* values = nullptr;  // blocks * 16 KB
+    const uint4* meta   = nullptr;  // blocks * 2 KB
+    const half*  B      = nullptr;  // [K][ld]
+    half*        C      = nullptr;  // [M][ld] fp16 result, used when C32 == nullptr
+    float*       C32    = nullptr;  // [M][N] fp32 result for a following residual product, or nullptr
+    float*       slots  = nullptr;  // fp32 partial blocks of split rows
+    int          n        = 0;
+    int          blocks_k = 0;  // K / 128
+    int          m        = 0;
+    int          ld       = 0;
     Schedule     sched;
 };
 

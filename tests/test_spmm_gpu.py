@@ -187,10 +187,12 @@ def test_token_major_layout(sp, oracle, torch_cuda, case):
     assert np.array_equal(C, run_spmm(sp, torch, words, offsets, B, M, N, K, 8))
 
 
-@pytest.mark.parametrize("case", [(512, 1024, 128, 0.8), (1152, 2304, 256, 0.7), (2304, 1152, 512, 0.5)],
-                         ids=["N128", "N256", "N512"])
+@pytest.mark.parametrize("case", [(512, 1024, 128, 0.8), (1152, 2304, 256, 0.7), (2304, 1152, 512, 0.5),
+                                  (1024, 1024, 192, 0.8), (2304, 4608, 384, 0.8), (4608, 9216, 1024, 0.6)],
+                         ids=["N128", "N256", "N512", "N192", "N384", "N1024"])
 def test_wide_n_in_column_blocks(sp, oracle, torch_cuda, case):
-    """N beyond the reference's 64 (prefill sizes): multiples of 64, one 64-column block per blockIdx.y."""
+    """N beyond the reference's 64 (prefill sizes): multiples of 64, served in column blocks of 256, 128 or
+    64 columns (the widest that divides N), one block per blockIdx.y."""
     M, K, N, p = case
     A = sp.synth_fp16((M, K), 500 + N, 0.02, p)
     B = sp.synth_fp16((K, N), 600 + N, 1.0, 0.0)
@@ -198,7 +200,7 @@ def test_wide_n_in_column_blocks(sp, oracle, torch_cuda, case):
     C = run_spmm(sp, torch_cuda, words, offsets, B, M, N, K, 4)
     ok, max_ratio, mean_rel = oracle.tolerance_check(C, oracle.spmm_f64(A, B))
     assert ok, (max_ratio, mean_rel)
-    # each 64-column block is the N = 64 product of that block of B (the partition may differ, hence a tolerance)
+    # a 64-column slice equals the N = 64 product of that slice of B (the partition may differ, hence a tolerance)
     block = run_spmm(sp, torch_cuda, words, offsets, np.ascontiguousarray(B[:, 64:128]), M, 64, K, 4)
     a, b = C[:, 64:128].view(np.float16).astype(np.float64), block.view(np.float16).astype(np.float64)
     assert np.abs(a - b).max() <= 2e-3 * np.abs(b).max()
