@@ -30,6 +30,7 @@ struct DecodeConfig {
     static constexpr int S    = N <= 64 ? 8 : (N == 128 ? 6 : 4);  // ring slots
     static constexpr int BBUF = 1;                 // B buffers per ring slot
     static constexpr int WTMA = N == 64 ? 0 : 1;   // words staged through shared memory by bulk copy
+    static constexpr int R    = D;  // staging buffers for the words: one per team (a shared ring of 9-11 measured slower)
 };
 
 struct DeviceInfo {
@@ -93,6 +94,25 @@ cudaError_t launch_ablated(cudaStream_t stream, const DecodeParams& params)
     kern<<<params.sched.num_ctas, decode_threads<D, Q, 1>(), smem, stream>>>(params);
     return cudaGetLastError();
 }
+template<int R, int PFR = 2, int ABL = 0>
+cudaError_t launch_staging_ring(cudaStream_t stream, const DecodeParams& params)
+{
+    constexpr int D = 8, Q = 4;
+    constexpr int smem = decode_smem_bytes<16, D, 1, word_stage_bytes<R, 1, 14>()>();
+    auto          kern = spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, 1, D, 1, PFR, R>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    kern<<<params.sched.num_ctas, decode_threads<D, Q, 1>(), smem, stream>>>(params);
+    return cudaGetLastError();
+}
+template<int D, int Q>
+cudaError_t launch_two_warp_teams(cudaStream_t stream, const DecodeParams& params)
+{
+    constexpr int smem = decode_smem_bytes<16, D, 1, word_stage_bytes<D, 2, 7>()>();
+    auto          kern = spmm_decode_kernel<16, D, Q, 2, 7, 0, 0, 1, D, 1>;
+    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    kern<<<params.sched.num_ctas, decode_threads<D, Q, 2>(), smem, stream>>>(params);
+    return cudaGetLastError();
+}
 template<int D, int Q, int S, int BBUF, int WTMA>
 cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, int abl)
 {
@@ -115,10 +135,11 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
         switch (envc ? atoi(envc) : 0) {
             case 1: return launch_ablated_d<8, 4, 8, 2, 0>(stream, params, abl);
             case 3: return launch_ablated_d<8, 4, 8, 1, 1>(stream, params, abl);
-            case 4: return launch_ablated_d<6, 3, 9, 1, 1>(stream, params, abl);
-            case 5: return launch_ablated_d<6, 2, 10, 1, 1>(stream, params, abl);
-            case 6: return launch_ablated_d<6, 4, 8, 1, 1>(stream, params, abl);
-            case 7: return launch_ablated_d<4, 2, 10, 1, 1>(stream, params, abl);
+            case 4: return launch_staging_ring<11, 1>(stream, params);
+            case 5: return launch_staging_ring<11, 3>(stream, params);
+            case 6: return launch_staging_ring<11, 4>(stream, params);
+            case 7: return launch_staging_ring<11, 3, 3>(stream, params);
+            case 8: return launch_staging_ring<8, 2, 3>(stream, params);
             default: break;
         }
     }
@@ -127,9 +148,9 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
     constexpr int smem =
-        decode_smem_bytes<NB, Cfg::S, Cfg::BBUF, Cfg::WTMA ? word_stage_bytes<D, Cfg::WPT, Cfg::VPL>() : 0>();
+        decode_smem_bytes<NB, Cfg::S, Cfg::BBUF, Cfg::WTMA ? word_stage_bytes<Cfg::R, Cfg::WPT, Cfg::VPL>() : 0>();
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, TM, Cfg::BBUF, Cfg::S, Cfg::WTMA>;
+    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, TM, Cfg::BBUF, Cfg::S, Cfg::WTMA, 2, Cfg::R>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {

@@ -173,6 +173,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 //       into registers directly.  Register loads are tracked in L1, whose size (what the shared
 //       memory carve-out leaves) then bounds the bytes in flight; the copy engine has no such bound.
 // PFR : a team asks for the words of its tile PFR rounds ahead (tile l + PFR * D) to be brought into L2.
+// R   : staging buffers for the words (WTMA; 0 = D).  Tile l of the chunk lands in buffer l % R; the
+//       team that has just emptied a buffer (tile l) asks for tile l + R into it, so R tiles are in
+//       flight per block whichever team will consume them.  The copy of a tile is then issued R
+//       tiles, not one round of D tiles, before it is needed.
 // BBUF : B buffers per slot.  2: the next tile's slice is fetched while this one is decoded (needs
 //       S == D); 1: the slice is fetched after the slot has been handed back.
 // ABL : debugging ablation mask (0 in production): 1 no clearing, 2 no scatter, 4 no word loads,
@@ -180,12 +184,14 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // TM : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
 //      library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
 //      k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TM = 0, int BBUF = 2, int S_ = 0, int WTMA = 0, int PFR = 2>
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TM = 0, int BBUF = 2, int S_ = 0, int WTMA = 0, int PFR = 2, int R_ = 0>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
     constexpr int NB = N < 16 ? 16 : N;
     constexpr int S  = S_ == 0 ? D : S_;
+    constexpr int R  = R_ == 0 ? D : R_;
+    static_assert(R >= D, "every team starts with a staged tile of its own");
     using BT         = BTile<NB>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
@@ -193,17 +199,21 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const uint32_t b_base    = a_base + S * kATileBytes;
     const uint32_t w_base    = b_base + BBUF * S * BT::kBytes;  // word staging, one buffer per team
     constexpr int  kStageBytes = WPT * VPL * 32 * 16;
-    const uint32_t bar_base  = w_base + (WTMA ? D * kStageBytes : 0);
+    const uint32_t bar_base  = w_base + (WTMA ? R * kStageBytes : 0);
     // barrier map (8 bytes each): [0,S) tile full, [S,2S) tile free, then acc full x2, acc free x2
     auto tile_full = [&](int s) { return bar_base + 8u * s; };
     auto tile_free = [&](int s) { return bar_base + 8u * (S + s); };
     auto acc_full  = [&](int b) { return bar_base + 8u * (2 * S + b); };
     auto acc_free  = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
     auto words_full = [&](int t) { return bar_base + 8u * (2 * S + 4 + t); };
-    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4 + D);
+    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4 + R);
     uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
     volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
+    // rounds[b]: how many times staging buffer b has been handed back to the copy engine.  A team may
+    // reach its wait for tile l before the previous tile of that buffer has even landed; the barrier's
+    // parity cannot tell those two phases apart, this counter can.
+    volatile uint32_t* rounds = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr + 8 - smem_base));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -219,20 +229,22 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     static_assert(S % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
     static_assert(S >= D, "every team needs a slot of its own to start with");
     static_assert(BBUF == 1 || S == D, "fetching the next B slice early needs a slot that stays with its team");
-    static_assert(8 * (2 * S + 4 + D) + 8 <= 512, "barrier block");
+    static_assert(8 * (2 * S + 4 + R) + 8 + 4 * R <= 512, "barrier block");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             ptx::mbar_init(tile_full(s), WPT);
             ptx::mbar_init(tile_free(s), 1);
         }
-        for (int t = 0; t < D; t++)
+        for (int t = 0; t < R; t++)
             ptx::mbar_init(words_full(t), 1);
         for (int b = 0; b < 2; b++) {
             ptx::mbar_init(acc_full(b), Q);
             ptx::mbar_init(acc_free(b), kEpilogueWarps);
         }
         *abort_word = 0;
+        for (int t = 0; t < R; t++)
+            rounds[t] = 0;
         ptx::mbar_init_fence();
     }
     // Clear the ring once: A buffers are kept all-zero between tiles, and columns N..NB-1 of the
@@ -317,21 +329,26 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 }
         };
         // WTMA: the first VPL * WPT * 32 vectors of a tile come through the team's staging buffer.
-        const uint32_t stage   = w_base + s_own * kStageBytes;
-        bool           pending = false;  // a bulk copy into the staging buffer has not been waited for
-        uint32_t       wphase  = 0;      // completed waits on this team's words_full barrier
-        auto fetch_words = [&](const uint4* from, int count) {
-            pending = true;
+        int pending_tile = -1;  // last tile this team asked the copy engine for (chunk-local), if any
+        // asks for the words of chunk-local tile `tile` (vectors off0 .. off1) into buffer tile % R
+        auto fetch_words = [&](int tile, int off0, int off1) {
+            pending_tile = tile;
             if (h == 0 && lane == 0) {
-                const uint32_t bytes = static_cast<uint32_t>(min(count, VPL * WPT * 32)) * 16u;
+                const uint32_t bar   = words_full(tile % R);
+                const uint32_t bytes = static_cast<uint32_t>(min(off1 - off0, VPL * WPT * 32)) * 16u;
                 if (bytes > 0 && !(ABL & 4)) {
-                    ptx::mbar_arrive_expect_tx(words_full(s_own), bytes);
-                    ptx::bulk_copy_g2s(stage, from, bytes, words_full(s_own));
+                    ptx::mbar_arrive_expect_tx(bar, bytes);
+                    ptx::bulk_copy_g2s(w_base + (tile % R) * kStageBytes, p.words + off0, bytes, bar);
                 }
                 else
-                    ptx::mbar_arrive(words_full(s_own));
+                    ptx::mbar_arrive(bar);
+                if (R != D) {
+                    __threadfence_block();
+                    rounds[tile % R] = static_cast<uint32_t>(tile / R);  // the barrier is armed for this round
+                }
             }
         };
+        uint32_t stage = w_base + (s_own % R) * kStageBytes;  // buffer of the tile being decoded
         auto take_words = [&](int count) {
             uint32_t seen = 0;
 #pragma unroll
@@ -352,6 +369,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // tile l + 2D can be requested into L2 while tile l is being decoded; the register loads of
         // tile l + D, issued after this tile's scatter, then find their lines in L2.
         int  after0 = 0, after1 = 0, pf0 = 0, pf1 = 0;
+        int  ring0 = 0, ring1 = 0;  // offsets of tile l + R, read one iteration before they are used
         auto prefetch_tile = [&](int off0, int off1) {
             if (h == 0 && lane == 0 && off1 > off0)
                 ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
@@ -361,8 +379,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const int off1 = __ldg(p.tile_offsets + tile_begin + s_own + 1);
             nvec           = off1 - off0;
             src            = p.words + off0 + lane_vec;
-            if (WTMA)
-                fetch_words(p.words + off0, nvec);
+            if (WTMA) {
+                fetch_words(s_own, off0, off1);
+                // the buffers beyond the first round: tiles s_own + D, s_own + 2 D, ... below R
+#pragma unroll 1
+                for (int t = s_own + D; t < R && t < num_tiles; t += D)
+                    fetch_words(t, __ldg(p.tile_offsets + tile_begin + t), __ldg(p.tile_offsets + tile_begin + t + 1));
+            }
             else
                 load_words(src, nvec);
             if (BBUF == 2)
@@ -383,6 +406,10 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     prefetch_tile(__ldg(p.tile_offsets + tile_begin + s_own + k * D),
                                   __ldg(p.tile_offsets + tile_begin + s_own + k * D + 1));
         }
+        if (WTMA && R != D && s_own + R < num_tiles) {
+            ring0 = __ldg(p.tile_offsets + tile_begin + s_own + R);
+            ring1 = __ldg(p.tile_offsets + tile_begin + s_own + R + 1);
+        }
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (s_own == 0 && h == 0)
             SPMM_TRACE(1);  // first loads issued
@@ -398,13 +425,37 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 prefetch_tile(pf0, pf1);  // tile l + PFR * D; its offsets were requested one iteration ago
             if (WTMA) {
                 // this tile's words: staging buffer -> registers, then the buffer takes the next tile
-                if (!ptx::mbar_wait_bounded(words_full(s_own), wphase & 1, abort_word)) {
+                stage = w_base + (l % R) * kStageBytes;
+                bool armed = true;
+                if (R != D && l >= R) {
+                    // wait until the buffer has been handed back for this round (it nearly always has)
+                    const uint32_t want  = static_cast<uint32_t>(l / R);
+                    uint64_t       start = 0;
+#pragma unroll 1
+                    for (uint32_t polls = 0; rounds[l % R] < want; polls++) {
+                        if (*abort_word != 0) {
+                            armed = false;
+                            break;
+                        }
+                        if ((polls & 1023u) == 1023u) {
+                            const uint64_t now = ptx::global_timer_ns();
+                            if (start == 0)
+                                start = now;
+                            else if (now - start > ptx::kWaitLimitNs) {
+                                *abort_word = 1;
+                                armed       = false;
+                                break;
+                            }
+                        }
+                    }
+                }
+                if (!armed || !ptx::mbar_wait_bounded(words_full(l % R), (l / R) & 1, abort_word)) {
                     if (WPT > 1)
                         asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
                     break;
                 }
-                pending = false;
-                ++wphase;
+                if (pending_tile == l)
+                    pending_tile = -1;
                 SPMM_FINE(fine, 8);
                 take_words(nvec);
                 // With two warps per team the copy engine's next write into the staging buffer is
@@ -413,8 +464,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 if (WPT > 1)
                     ptx::fence_proxy_async_smem();
                 team_sync();
-                if (has_next)
-                    fetch_words(p.words + next0, next1 - next0);
+                // the emptied buffer takes tile l + R (this team's own next tile when R == D)
+                if (l + R < num_tiles) {
+                    if (R == D)
+                        fetch_words(l + R, next0, next1);
+                    else
+                        fetch_words(l + R, ring0, ring1);
+                }
                 SPMM_FINE(fine, 9);
             }
             if (lap > 0) {
@@ -468,6 +524,10 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     after1 = __ldg(p.tile_offsets + tile_begin + l + 3 * D + 1);
                 }
             }
+            if (WTMA && R != D && l + D + R < num_tiles) {
+                ring0 = __ldg(p.tile_offsets + tile_begin + l + D + R);
+                ring1 = __ldg(p.tile_offsets + tile_begin + l + D + R + 1);
+            }
             pf0 = pf1 = 0;
             if (l + (PFR + 1) * D < num_tiles) {
                 pf0 = __ldg(p.tile_offsets + tile_begin + l + (PFR + 1) * D);
@@ -491,8 +551,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             a_tile = a_base + slot * kATileBytes;
         }
         ptx::cp_async_wait_all();
-        if (WTMA && pending)  // only on the way out of an abandoned block
-            ptx::mbar_wait_quiet(words_full(s_own), wphase & 1, 1000000ull);
+        if (WTMA && pending_tile >= 0)  // only on the way out of an abandoned block
+            ptx::mbar_wait_quiet(words_full(pending_tile % R), (pending_tile / R) & 1, 1000000ull);
         if (s_own == 0 && h == 0)
             SPMM_TRACE(6);
     }
