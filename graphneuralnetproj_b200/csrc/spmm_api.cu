@@ -140,6 +140,9 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
             case 6: return launch_staging_ring<11, 4>(stream, params);
             case 7: return launch_staging_ring<11, 3, 3>(stream, params);
             case 8: return launch_staging_ring<8, 2, 3>(stream, params);
+            case 9: return launch_staging_ring<8, 0>(stream, params);
+            case 10: return launch_staging_ring<11, 0>(stream, params);
+            case 11: return launch_staging_ring<8, 0, 3>(stream, params);
             default: break;
         }
     }
@@ -554,6 +557,35 @@ int spmm_b200_spmm_splitk(void*       stream,
                                             K_Global,
                                             static_cast<half*>(Reduction_Workspace),
                                             Split_K));
+}
+
+int spmm_b200_spmm_splitk_host_io(void*       stream,
+                                  const void* Compressed_A,
+                                  const int*  TileOffsets,
+                                  const void* B_host,
+                                  void*       C_host,
+                                  void*       B_dev,
+                                  void*       C_dev,
+                                  int         M_Global,
+                                  int         N_Global,
+                                  int         K_Global,
+                                  void*       Reduction_Workspace,
+                                  int         Split_K)
+{
+    if (!B_host || !C_host || !B_dev || !C_dev || M_Global <= 0 || N_Global <= 0 || K_Global <= 0)
+        return static_cast<int>(cudaErrorInvalidValue);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    cudaError_t  e  = cudaMemcpyAsync(B_dev, B_host, static_cast<size_t>(K_Global) * N_Global * sizeof(half),
+                                      cudaMemcpyHostToDevice, st);
+    if (e != cudaSuccess)
+        return static_cast<int>(e);
+    e = SpMM_SplitK_API(st, nullptr, static_cast<const uint4*>(Compressed_A), nullptr, nullptr, TileOffsets,
+                        static_cast<const half*>(B_dev), static_cast<half*>(C_dev), M_Global, N_Global, K_Global,
+                        static_cast<half*>(Reduction_Workspace), Split_K);
+    if (e != cudaSuccess)
+        return static_cast<int>(e);
+    return static_cast<int>(cudaMemcpyAsync(C_host, C_dev, static_cast<size_t>(M_Global) * N_Global * sizeof(half),
+                                            cudaMemcpyDeviceToHost, st));
 }
 
 int spmm_b200_spmm_splitk_token_major(void*       stream,

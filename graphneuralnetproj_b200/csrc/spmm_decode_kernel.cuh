@@ -172,7 +172,8 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 //       team, completion on an mbarrier) and are then read into registers, instead of being loaded
 //       into registers directly.  Register loads are tracked in L1, whose size (what the shared
 //       memory carve-out leaves) then bounds the bytes in flight; the copy engine has no such bound.
-// PFR : a team asks for the words of its tile PFR rounds ahead (tile l + PFR * D) to be brought into L2.
+// PFR : a team asks for the words of its tile PFR rounds ahead (tile l + PFR * D) to be brought into L2
+//       (0 = no such requests).
 // R   : staging buffers for the words (WTMA; 0 = D).  Tile l of the chunk lands in buffer l % R; the
 //       team that has just emptied a buffer (tile l) asks for tile l + R into it, so R tiles are in
 //       flight per block whichever team will consume them.  The copy of a tile is then issued R
@@ -371,7 +372,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         int  after0 = 0, after1 = 0, pf0 = 0, pf1 = 0;
         int  ring0 = 0, ring1 = 0;  // offsets of tile l + R, read one iteration before they are used
         auto prefetch_tile = [&](int off0, int off1) {
-            if (h == 0 && lane == 0 && off1 > off0)
+            if (PFR > 0 && h == 0 && lane == 0 && off1 > off0)
                 ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
         };
         if (s_own < num_tiles) {

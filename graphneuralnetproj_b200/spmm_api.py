@@ -41,6 +41,8 @@ def _load():
     lib.spmm_b200_spmm_splitk.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_void_p] + [ctypes.c_void_p] * 2 + \
         [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
     lib.spmm_b200_spmm_splitk.restype = ctypes.c_int
+    lib.spmm_b200_spmm_splitk_host_io.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
+    lib.spmm_b200_spmm_splitk_host_io.restype = ctypes.c_int
     lib.spmm_b200_spmm_own_scratch.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3
     lib.spmm_b200_spmm_own_scratch.restype = ctypes.c_int
     lib.spmm_b200_spmm_splitk_token_major.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
@@ -135,6 +137,23 @@ def SpMM_SplitK_API(stream, A, Compressed_A, A1_Ind_data, metadata, TileOffsets,
     return LIB.spmm_b200_spmm_splitk(ctypes.c_void_p(handle), _dev_ptr(A), _dev_ptr(Compressed_A), _dev_ptr(A1_Ind_data),
                                      _dev_ptr(metadata), _dev_ptr(TileOffsets), _dev_ptr(B), _dev_ptr(C), M_Global,
                                      N_Global, K_Global, _dev_ptr(Reduction_Workspace), Split_K)
+
+
+def SpMM_SplitK_API_host_io(stream, Compressed_A, TileOffsets, B_host, C_host, B_dev, C_dev, M_Global, N_Global, K_Global,
+                            Reduction_Workspace, Split_K):
+    """SpMM_SplitK_API for activations and results in (page-locked) host memory: one call that copies
+    B_host to B_dev, multiplies and copies C_dev to C_host, all on `stream`.  B_host / C_host: CPU
+    tensors; the rest CUDA tensors.  Returns the first cudaError_t met as an int."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    handle = stream if isinstance(stream, int) else stream.cuda_stream
+    if B_host.is_cuda or C_host.is_cuda:
+        raise ValueError("B_host and C_host must be CPU tensors")
+    return LIB.spmm_b200_spmm_splitk_host_io(ctypes.c_void_p(handle), _dev_ptr(Compressed_A), _dev_ptr(TileOffsets),
+                                             ctypes.c_void_p(B_host.data_ptr()), ctypes.c_void_p(C_host.data_ptr()),
+                                             _dev_ptr(B_dev), _dev_ptr(C_dev), M_Global, N_Global, K_Global,
+                                             _dev_ptr(Reduction_Workspace), Split_K)
 
 
 def SpMM_SplitK_API_token_major(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,

@@ -49,6 +49,25 @@ int spmm_b200_spmm_splitk(void*       stream,
                           void*       Reduction_Workspace,
                           int         Split_K);
 
+/* spmm_b200_spmm_splitk (unstructured mode) for activations and results that live in host memory,
+ * as the reference's harness holds them around its cudaMemcpy calls (kernel_benchmark/
+ * spmm_test.cu:118-137, 520-533): on `stream`, copies B_host[K][N] to B_dev, multiplies, copies
+ * C_dev[M][N] to C_host.  B_dev and C_dev are device buffers of K*N and M*N halves provided by the
+ * caller (nothing is allocated here); B_host and C_host should be page-locked for the copies to be
+ * asynchronous.  Returns the first cudaError_t met, as an int. */
+int spmm_b200_spmm_splitk_host_io(void*       stream,
+                                  const void* Compressed_A,
+                                  const int*  TileOffsets,
+                                  const void* B_host,
+                                  void*       C_host,
+                                  void*       B_dev,
+                                  void*       C_dev,
+                                  int         M_Global,
+                                  int         N_Global,
+                                  int         K_Global,
+                                  void*       Reduction_Workspace,
+                                  int         Split_K);
+
 /* The eleven-argument upstream form of SpMM_SplitK_API that the reference's FasterTransformer
  * glue calls (third_party/ft.patch:2822-2846), with token-major layouts: B[N][K], C[N][M]. */
 int spmm_b200_spmm_splitk_token_major(void*       stream,

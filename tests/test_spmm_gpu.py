@@ -206,6 +206,28 @@ def test_wide_n_in_column_blocks(sp, oracle, torch_cuda, case):
     assert np.abs(a - b).max() <= 2e-3 * np.abs(b).max()
 
 
+def test_host_buffer_entry_point(sp, oracle, torch_cuda):
+    """The C call that takes B and C in page-locked host memory gives the result of the device-pointer call."""
+    torch = torch_cuda
+    dev = torch.device("cuda:0")
+    M, K, N, sk = 1152, 2304, 16, 8
+    A = sp.synth_fp16((M, K), 901, 0.02, 0.8)
+    B = sp.synth_fp16((K, N), 902, 1.0, 0.0)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    want = run_spmm(sp, torch, words, offsets, B, M, N, K, sk)
+    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    od = torch.from_numpy(offsets).to(dev)
+    B_host = torch.from_numpy(B.view(np.int16)).pin_memory()
+    C_host = torch.zeros((M, N), dtype=torch.int16).pin_memory()
+    B_dev = torch.zeros((K, N), dtype=torch.int16, device=dev)
+    C_dev = torch.zeros((M, N), dtype=torch.int16, device=dev)
+    ws = torch.zeros(sp.workspace_bytes(M, N, sk) // 2, dtype=torch.int16, device=dev)
+    rc = sp.SpMM_SplitK_API_host_io(None, wd, od, B_host, C_host, B_dev, C_dev, M, N, K, ws, sk)
+    torch.cuda.synchronize()
+    assert rc == 0
+    assert np.array_equal(C_host.numpy().view(np.uint16), want)
+
+
 def test_a_wait_that_runs_out_is_reported_not_hung(sp, oracle, torch_cuda):
     """Failure detection without a fault: a kernel waits on a barrier nothing arrives on; the bounded
     wait gives up after 50 ms, the kernel returns, the status word says so, and the device keeps working."""
