@@ -367,10 +367,13 @@ def run_sweep(args):
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
     peak, _ = measured_hbm_peak()
-    shapes = [(n, m, k) for n, m, k, _ in LAYERS if n in args.sweep_layers.split(",")]
+    # "cfg1" = the reference's single-SpMM case (M = K = 7168 with its Split_K hint 5), beside the OPT-66B layers
+    shapes = [(n, m, k, 8) for n, m, k, _ in LAYERS if n in args.sweep_layers.split(",")]
+    if "cfg1" in args.sweep_layers.split(","):
+        shapes.append(("cfg1", 7168, 7168, 5))
     n_list = [int(x) for x in args.sweep_n.split(",")]
     p_list = [float(x) for x in args.sweep_p.split(",")]
-    for name, M, K in shapes:
+    for name, M, K, sk in shapes:
         for p in p_list:
             A = sp.synth_fp16((M, K), 0xA100 + int(p * 100), 0.02, p)
             words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, 16, K)
@@ -384,10 +387,10 @@ def run_sweep(args):
             for N in n_list:
                 Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB100, 1.0).view(np.int16)).to(dev)
                 Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
-                ws = torch.zeros(sp.workspace_bytes(M, N, 8) // 2, dtype=torch.int16, device=dev)
+                ws = torch.zeros(sp.workspace_bytes(M, N, sk) // 2, dtype=torch.int16, device=dev)
 
                 def ours(i):
-                    rc = sp.SpMM_SplitK_API(None, None, wds[i % copies], None, None, od, Bd, Cd, M, N, K, ws, 8)
+                    rc = sp.SpMM_SplitK_API(None, None, wds[i % copies], None, None, od, Bd, Cd, M, N, K, ws, sk)
                     assert rc == 0, rc
 
                 def cublas(i):
@@ -474,6 +477,79 @@ def run_prefill(args):
             del wd, Ad
             torch.cuda.empty_cache()
     assert sp.device_status() == 0
+
+
+def run_row_parallel(args):
+    """Row-parallel (by K) layer across the GPUs of the box: every rank multiplies its K shard of an
+    FFN2-shaped layer (M = 9216, 36864 columns of A per rank) and one NCCL sum all-reduce of the M x N
+    result finishes it.  Prints one JSON line with the SpMM-only and the SpMM + reduce time (device-timed,
+    max over ranks)."""
+    import torch
+    import torch.distributed as dist
+
+    import graphneuralnetproj_b200 as sp
+    from graphneuralnetproj_b200.tensor_parallel import RowParallelSpMM
+
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    M, K_shard, N = 9216, 36864, N_TOKENS
+    words, offsets, n_offsets = make_layer(sp, "ffn2", M, K_shard, 0xA500 + rank)
+    wbytes = 4 * words.size + 4 * n_offsets
+    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    od = torch.from_numpy(offsets).to(dev)
+    Bd = torch.from_numpy(sp.synth_fp16((K_shard, N), 0xB500 + rank, 1.0).view(np.int16)).to(dev)
+    layer = RowParallelSpMM(wd, od, M, N, K_shard, split_k=8)
+    # a second layer's worth of weights between timed launches keeps the first one out of L2
+    other = RowParallelSpMM(wd.clone(), od, M, N, K_shard, split_k=8)
+
+    def timed(fn):
+        for _ in range(max(args.warmup, 3)):
+            fn()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(args.steps):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return float(t.item())
+
+    def spmm_only():
+        for l in (layer, other):
+            rc = sp.SpMM_SplitK_API(None, None, l.words, None, None, l.offsets, Bd, l.C, M, N, K_shard, l.workspace, 8)
+            assert rc == 0
+
+    def with_reduce():
+        for l in (layer, other):
+            l.forward(Bd)
+
+    ms_spmm = timed(spmm_only) / 2
+    ms_full = timed(with_reduce) / 2
+    assert sp.device_status() == 0
+    if rank == 0:
+        peak, src = measured_hbm_peak()
+        print(json.dumps({
+            "metric": "effective weight-HBM GB/s, row-parallel SpMM + all-reduce (FFN2 shape, N=16, 80% sparse)",
+            "value": round(world * wbytes / (ms_full * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
+            "steps": args.steps, "warmup": max(args.warmup, 3), "scaling": "weak", "higher_is_better": True,
+            "spmm_only_us": round(ms_spmm * 1e3, 2), "spmm_plus_allreduce_us": round(ms_full * 1e3, 2),
+            "spmm_only_gbs_per_gpu": round(wbytes / (ms_spmm * 1e-3) / 1e9, 1),
+            "allreduce_bytes": M * N * 2,
+            "config": {"workload": "row_parallel_ffn2", "M": M, "K_per_rank": K_shard, "n_tokens": N, "sparsity": SPARSITY,
+                       "parallelism": "row-parallel by K x%d, NCCL sum all-reduce of fp16 C" % world},
+            "roofline_frac_spmm_only": round(wbytes / (ms_spmm * 1e-3) / 1e9 / peak, 4), "peak_source": src}))
+    if world > 1:
+        dist.destroy_process_group()
 
 
 def prune_2_of_4(A_bits, keep_prob, seed):
@@ -591,10 +667,13 @@ def main():
     ap.add_argument("--prefill", action="store_true", help="prefill-size points (N >= 256) instead of the bench line")
     ap.add_argument("--prefill-n", default="256,512,1024,2048")
     ap.add_argument("--small", action="store_true", help="with --prefill: only the 12288 x 12288 shape")
+    ap.add_argument("--row-parallel", action="store_true", help="row-parallel (by K) layer with an NCCL all-reduce, one rank per GPU")
     ap.add_argument("--hetero", action="store_true", help="heterogeneous decomposition points (structured half on the sparse tensor core)")
     ap.add_argument("--hetero-size", type=int, default=12288)
     args = ap.parse_args()
-    if args.hetero:
+    if args.row_parallel:
+        run_row_parallel(args)
+    elif args.hetero:
         run_hetero(args)
     elif args.prefill:
         run_prefill(args)

@@ -166,6 +166,33 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     return cudaGetLastError();
 }
 
+
+// Scratch for the fp32 partial tiles of split rows, for callers that cannot provide a workspace.
+// It lives in the library image: every GPU that loads the library holds these 10 MiB until the
+// process exits.  In host code the name below is only a handle; the device address comes from
+// cudaGetSymbolAddress.
+constexpr size_t kOwnScratchBytes = 10u << 20;
+static __device__ __align__(256) float g_own_scratch[kOwnScratchBytes / sizeof(float)];
+
+// Device address of g_own_scratch on `device` (which must be current), looked up once per device.
+cudaError_t own_scratch_address(int device, float** out)
+{
+    static float*     address[64] = {};
+    static std::mutex lock;
+    std::lock_guard<std::mutex> guard(lock);
+    float*& slot = address[device & 63];
+    if (slot == nullptr) {
+        void*       p = nullptr;
+        cudaError_t e = cudaGetSymbolAddress(&p, g_own_scratch);
+        if (e != cudaSuccess)
+            return e;
+        slot = static_cast<float*>(p);
+    }
+    *out = slot;
+    return cudaSuccess;
+}
+
+
 bool aligned16(const void* p)
 {
     return (reinterpret_cast<uintptr_t>(p) & 15u) == 0;
@@ -219,6 +246,23 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.B            = B;
     params.C            = C;
     params.slots        = reinterpret_cast<float*>(reinterpret_cast<char*>(Reduction_Workspace) + workspace_skip_bytes);
+    long slots_granted  = slots;
+    if (!wide) {
+        // A workspace sized by a small Split_K hint (the reference's 7168 x 7168 case passes 5) cannot
+        // hold the partial tiles of a partition over all SMs; the library's built-in scratch takes its
+        // place when it holds more.
+        const Schedule& all_sms = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, 1L << 40});
+        const long      own     = static_cast<long>(kOwnScratchBytes / (static_cast<size_t>(kTileRows) * n_block * sizeof(float)));
+        if (slots < all_sms.slots_used && own > slots) {
+            float* scratch = nullptr;
+            if (own_scratch_address(device, &scratch) == cudaSuccess) {
+                params.slots  = scratch;
+                slots_granted = own;
+            }
+            else
+                (void)cudaGetLastError();
+        }
+    }
     params.addend       = addend;
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
@@ -226,7 +270,7 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.ld           = N_Global;
     // with several column blocks the blocks of one column share the SMs with the other columns
     params.sched = cached_schedule(PlanKey{
-        tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots});
+        tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots_granted});
     params.slots_per_block_column = params.sched.slots_used;
     if (wide) {
         switch (n_block) {
@@ -391,36 +435,6 @@ cudaError_t SpMM_SplitK_API(cudaStream_t stream,
 }
 
 // ------------------------------------------------------------------ entry point that allocates nothing
-namespace spmm_b200 {
-namespace {
-
-// Scratch for the fp32 partial tiles of split rows, for callers that cannot provide a workspace.
-// It lives in the library image: every GPU that loads the library holds these 10 MiB until the
-// process exits.  In host code the name below is only a handle; the device address comes from
-// cudaGetSymbolAddress.
-constexpr size_t kOwnScratchBytes = 10u << 20;
-static __device__ __align__(256) float g_own_scratch[kOwnScratchBytes / sizeof(float)];
-
-// Device address of g_own_scratch on `device` (which must be current), looked up once per device.
-cudaError_t own_scratch_address(int device, float** out)
-{
-    static float*     address[64] = {};
-    static std::mutex lock;
-    std::lock_guard<std::mutex> guard(lock);
-    float*& slot = address[device & 63];
-    if (slot == nullptr) {
-        void*       p = nullptr;
-        cudaError_t e = cudaGetSymbolAddress(&p, g_own_scratch);
-        if (e != cudaSuccess)
-            return e;
-        slot = static_cast<float*>(p);
-    }
-    *out = slot;
-    return cudaSuccess;
-}
-
-}  // namespace
-}  // namespace spmm_b200
 
 extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
                                           const void* Compressed_A,

@@ -419,6 +419,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         for (int l = s_own; l < num_tiles; l += D, ++use) {
             const bool has_next = l + D < num_tiles;
             const bool fine     = (s_own == 0 && h == 0 && use == 8);
+            (void)fine;
             const int  lap      = l / S;  // how often this slot has been filled before
             SPMM_FINE(fine, 0);
             SPMM_FINE(s_own == 0 && h == 0 && use == 9, 10);

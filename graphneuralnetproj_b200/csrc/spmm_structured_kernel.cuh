@@ -134,19 +134,23 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
 
     if (warp == kFirstMmaWarp + 1) {
         // ------------------------------------------------------------ producer: values and metadata
-        if (lane == 0) {
-            int issued = 0;
+        // Lane 0 copies the values, lane 1 the metadata, in one instruction: issuing a bulk copy
+        // costs the issuing thread a few hundred cycles, and one thread issuing both copies of every
+        // block would be close to the time a block may take at full memory bandwidth.
+        if (lane < 2) {
+            int            issued = 0;
+            const uint32_t bytes  = lane == 0 ? kBlockValueBytes : kBlockMetaBytes;
+            const uint32_t dst0   = lane == 0 ? a_base : e_base;
+            const uint4*   src0   = lane == 0 ? p.values : p.meta;
 #pragma unroll 1
             for (int l = 0; l < num_tiles; l++, issued++) {
                 const int s = l % STAGES, u = l / STAGES;
                 if (u > 0 && !ptx::mbar_wait_bounded(empty(s), (u - 1) & 1, abort_word))
                     break;
                 const size_t t = static_cast<size_t>(tile_begin + l);
-                ptx::mbar_arrive_expect_tx(ae_full(s), kBlockValueBytes + kBlockMetaBytes);
-                ptx::bulk_copy_g2s(a_base + s * kBlockValueBytes, p.values + t * (kBlockValueBytes / 16), kBlockValueBytes,
-                                   ae_full(s));
-                ptx::bulk_copy_g2s(e_base + s * kBlockMetaBytes, p.meta + t * (kBlockMetaBytes / 16), kBlockMetaBytes,
-                                   ae_full(s));
+                if (lane == 0)
+                    ptx::mbar_arrive_expect_tx(ae_full(s), kBlockValueBytes + kBlockMetaBytes);
+                ptx::bulk_copy_g2s(dst0 + s * bytes, src0 + t * (bytes / 16), bytes, ae_full(s));
             }
             if (*abort_word != 0) {
                 // copies that nobody will wait for any more must land before the block exits
