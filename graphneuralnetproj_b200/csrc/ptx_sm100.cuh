@@ -123,6 +123,19 @@ __device__ __forceinline__ bool mbar_wait_quiet(uint32_t bar, uint32_t parity, u
     }
 }
 
+// Programmatic dependent launch (a kernel launched with the programmatic-stream-serialization
+// attribute may start before its predecessor in the stream has finished).  Both are no-ops for a
+// kernel launched the ordinary way.
+__device__ __forceinline__ void grid_launch_dependents()
+{
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+// Blocks until the predecessor grid has completed and its memory operations are visible.
+__device__ __forceinline__ void grid_dependency_wait()
+{
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+
 // ---------------------------------------------------------------- copies
 // 16-byte asynchronous copy, bypassing L1.
 __device__ __forceinline__ void cp_async_16(uint32_t dst_smem, const void* src)

@@ -162,8 +162,20 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
         }
         dev.attrs_set[n_index] = true;
     }
-    kern<<<dim3(params.sched.num_ctas, column_blocks), decode_threads<D, Cfg::Q, Cfg::WPT>(), smem, stream>>>(params);
-    return cudaGetLastError();
+    // Launched so that it may start while the kernel before it in the stream drains (the kernel waits
+    // for its predecessor before touching anything but the weights).
+    cudaLaunchConfig_t config = {};
+    config.gridDim            = dim3(params.sched.num_ctas, column_blocks);
+    config.blockDim           = dim3(decode_threads<D, Cfg::Q, Cfg::WPT>());
+    config.dynamicSmemBytes   = smem;
+    config.stream             = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                       = attr;
+    config.numAttrs                                    = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kern, params);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 
@@ -321,8 +333,18 @@ cudaError_t launch_structured(cudaStream_t stream, DeviceInfo& dev, int n_index,
         }
         dev.attrs_set[n_index] = true;
     }
-    kern<<<params.sched.num_ctas, kStructuredThreads, smem, stream>>>(params);
-    return cudaGetLastError();
+    cudaLaunchConfig_t config = {};
+    config.gridDim            = dim3(params.sched.num_ctas);
+    config.blockDim           = dim3(kStructuredThreads);
+    config.dynamicSmemBytes   = smem;
+    config.stream             = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                       = attr;
+    config.numAttrs                                    = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kern, params);
+    return e != cudaSuccess ? e : cudaGetLastError();
 }
 
 // Heterogeneous product C = A1 * B + A2 * B: A1 (at most two nonzeros per aligned group of four along

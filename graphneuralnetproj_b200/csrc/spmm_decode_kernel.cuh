@@ -263,6 +263,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const uint32_t tmem_base = *tmem_slot;
     if (warp == 0)
         SPMM_TRACE(0);  // prologue done
+    // Programmatic dependent launch: the next kernel in the stream may be scheduled from here on (it
+    // still needs this block's resources to start on this SM).  This kernel in turn may have started
+    // before its predecessor finished: everything the predecessor may still be writing or reading --
+    // B, C, the workspace, the arrival counters -- is touched only after ptx::grid_dependency_wait();
+    // the weights and their offsets are not covered by that rule (they are constant during inference)
+    // and are requested before the wait.
+    ptx::grid_launch_dependents();
 
     if (warp >= kFirstDecodeWarp) {
         // ------------------------------------------------------------ decoder team
@@ -389,8 +396,6 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             }
             else
                 load_words(src, nvec);
-            if (BBUF == 2)
-                stage_b(j, 0);
             if (s_own + D < num_tiles) {
                 next0 = __ldg(p.tile_offsets + tile_begin + s_own + D);
                 next1 = __ldg(p.tile_offsets + tile_begin + s_own + D + 1);
@@ -411,6 +416,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             ring0 = __ldg(p.tile_offsets + tile_begin + s_own + R);
             ring1 = __ldg(p.tile_offsets + tile_begin + s_own + R + 1);
         }
+        ptx::grid_dependency_wait();
+        if (BBUF == 2 && s_own < num_tiles)
+            stage_b(j, 0);
         asm volatile("cp.async.commit_group;" ::: "memory");
         if (s_own == 0 && h == 0)
             SPMM_TRACE(1);  // first loads issued
@@ -460,11 +468,11 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     pending_tile = -1;
                 SPMM_FINE(fine, 8);
                 take_words(nvec);
-                // With two warps per team the copy engine's next write into the staging buffer is
-                // issued by the other warp: this warp's reads are ordered before it by a proxy fence
-                // on this side of the team barrier (without it results were wrong on the GPU).
-                if (WPT > 1)
-                    ptx::fence_proxy_async_smem();
+                // The copy engine's next write into the staging buffer must not overtake these reads:
+                // they are generic-proxy accesses that may still be queued in the load/store unit when
+                // the bulk copy is issued, so each reader fences before the team barrier (without the
+                // fence two-warp teams gave wrong results on the GPU).
+                ptx::fence_proxy_async_smem();
                 team_sync();
                 // the emptied buffer takes tile l + R (this team's own next tile when R == D)
                 if (l + R < num_tiles) {
@@ -565,6 +573,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // Every MMA warp arrives on the segment's acc_full barrier, through tcgen05.commit if it
         // issued anything for the segment and directly otherwise.
         const int q = warp - kFirstMmaWarp;
+        ptx::grid_dependency_wait();
         if (lane == 0) {
             constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(kTileRows, NB, false, TM ? false : true);
             const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
@@ -618,6 +627,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // ------------------------------------------------------------ epilogue
         const int row_in_tile = warp * 32 + lane;
         int       seg         = 0;
+        ptx::grid_dependency_wait();
 #pragma unroll 1
         for (int l = 0; l < num_tiles; ++seg) {
             const int  t0       = tile_begin + l;

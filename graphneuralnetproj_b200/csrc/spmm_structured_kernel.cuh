@@ -131,6 +131,9 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_e    = tmem_base + 2 * NB;
+    // Programmatic dependent launch, as in the decode kernel: the packed weights are requested at
+    // once, B, C, the workspace and the arrival counters only after the predecessor grid has finished.
+    ptx::grid_launch_dependents();
 
     if (warp == kFirstMmaWarp + 1) {
         // ------------------------------------------------------------ producer: values and metadata
@@ -174,6 +177,7 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
         };
         int  announced = 0;
         bool ok        = true;
+        ptx::grid_dependency_wait();
 #pragma unroll 1
         for (int l = 0; l < num_tiles; l++) {
             const int s = l % STAGES, u = l / STAGES;
@@ -257,6 +261,7 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
         // ------------------------------------------------------------ epilogue
         const int row_in_tile = warp * 32 + lane;
         int       seg         = 0;
+        ptx::grid_dependency_wait();
 #pragma unroll 1
         for (int l = 0; l < num_tiles; ++seg) {
             const int  t0       = tile_begin + l;
