@@ -37,8 +37,8 @@ SPARSITY = 0.8
 WORKLOAD = "opt66b_decoder_block_4_spmm_n16_p0.8"
 HBM_PEAK_FALLBACK_GBS = 6650.0
 # dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture summarised in
-# profiles/spmm_decode_n16_ffn1_outproj_full_capture.md (FFN1 launch: 277.16 MB / 273.0 MB)
-DRAM_TRAFFIC_OVER_ALGORITHMIC = 1.015
+# profiles/spmm_decode_n16_ffn1_lsu_counters.md (FFN1 launch: 278.5 MB / 273.5 MB)
+DRAM_TRAFFIC_OVER_ALGORITHMIC = 1.018
 
 
 def measured_hbm_peak():
@@ -244,7 +244,7 @@ def run_ours(args):
                      "frac": round(achieved / peak, 4),
                      "traffic": int(algo_bytes * DRAM_TRAFFIC_OVER_ALGORITHMIC),
                      "traffic_note": "bytes per step (4 launches): ncu dram read+write of one launch / its algorithmic "
-                                     "bytes = 1.015, applied to the step", "peak_source": peak_kind,
+                                     "bytes = 1.018 (FFN1: 278.5 MB against 273.5 MB), applied to the step", "peak_source": peak_kind,
                      "kernel": "spmm_decode_kernel<16>", "algorithmic_bytes_per_step": algo_bytes},
         "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
                 "h2d_bytes_per_step": sum(2 * L["K"] * N_TOKENS for L in layers),
