@@ -159,6 +159,26 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src
                  : "memory");
 }
 
+// Adds `bytes` to what the barrier's current phase expects from bulk copies, without arriving.
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes)
+{
+    asm volatile("mbarrier.expect_tx.relaxed.cta.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+// Tiled TMA load of one box of a 2-D tensor (x = innermost coordinate, in elements; x * element size
+// must be a multiple of 16 bytes).  `tensor_map` is the generic address of a CUtensorMap in
+// parameter or global memory.
+__device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar)
+{
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     dst_smem),
+                 "l"(tensor_map),
+                 "r"(x),
+                 "r"(y),
+                 "r"(bar)
+                 : "memory");
+}
+
 // Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2.
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes)
 {

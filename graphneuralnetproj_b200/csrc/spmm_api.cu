@@ -284,6 +284,30 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.sched = cached_schedule(PlanKey{
         tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots_granted});
     params.slots_per_block_column = params.sched.slots_used;
+    if (wide && n_block >= 128) {
+        // B slices of the wide forms come by tiled TMA loads: describe B[K][N] to the copy engine
+        using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+        static EncodeFn encode = nullptr;
+        if (encode == nullptr) {
+            void*                           fn     = nullptr;
+            cudaDriverEntryPointQueryResult status = cudaDriverEntryPointSymbolNotFound;
+            e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+            if (e != cudaSuccess || status != cudaDriverEntryPointSuccess || fn == nullptr)
+                return e != cudaSuccess ? e : cudaErrorNotSupported;
+            encode = reinterpret_cast<EncodeFn>(fn);
+        }
+        const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(N_Global), static_cast<cuuint64_t>(K_Global)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N_Global) * sizeof(half)};
+        const cuuint32_t box[2]     = {64, static_cast<cuuint32_t>(kTileCols)};
+        const cuuint32_t steps[2]   = {1, 1};
+        if (encode(&params.b_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(B), dims, strides, box, steps,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+    }
     if (wide) {
         switch (n_block) {
             case 256:

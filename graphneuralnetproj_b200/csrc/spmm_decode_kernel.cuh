@@ -42,6 +42,7 @@
 // released and a status word in global memory records the event.
 #pragma once
 
+#include <cuda.h>
 #include <cuda_fp16.h>
 
 #include "ptx_sm100.cuh"
@@ -92,6 +93,9 @@ struct DecodeParams {
     int          ld           = 0;  // row stride of B[K][ld] and C[M][ld] in halves (row-major layout): the full N
     int          slots_per_block_column = 0;  // workspace slots used by one column block (blockIdx.y)
     const float* addend = nullptr;  // optional fp32 [M][N] added before the rounding (row-major results, N <= 64 only)
+    // B as a 2-D tensor [K][ld] of halves with a 64 x 64 box and 128-byte swizzle: used by the 128- and
+    // 256-column forms, whose B slices arrive by tiled TMA loads instead of 16-byte copies
+    alignas(64) CUtensorMap b_map;
     Schedule     sched;
 };
 
@@ -286,12 +290,27 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // B staging: a 64 x N slice is kTileCols * N / 8 chunks of 16 bytes, contiguous in global
         // memory; this warp copies chunks first_chunk, first_chunk + WPT * 32, ...  Chunk c lands at
         // swizzle(row * row_bytes + col * 16) with row = c / chunks_per_row, col = c % chunks_per_row.
+        constexpr bool kBTma        = N >= 128 && !TM;
+        static_assert(!kBTma || BBUF == 1, "tiled loads of B go to the slot's only B buffer");
         constexpr int kChunksPerRow = N / 8;
         constexpr int kChunks       = kTileCols * kChunksPerRow;
         const int     first_chunk   = h * 32 + lane;
         auto stage_b = [&](int j, int parity) {
             if (ABL & 16)
                 return;
+            if (kBTma) {
+                // one box of 64 k rows x 64 columns per swizzle atom; the bytes are counted on the
+                // barrier the MMA warp waits on for this tile
+                if (h == 0 && lane == 0) {
+                    const uint32_t bar = tile_full(slot);
+                    ptx::mbar_expect_tx(bar, BT::kBytes);
+#pragma unroll
+                    for (int a = 0; a < BT::kAtoms; a++)
+                        ptx::tma_load_2d(b_base + slot * BT::kBytes + a * BT::kAtomBytes, &p.b_map,
+                                         static_cast<int>(blockIdx.y) * N + a * 64, j * kTileCols, bar);
+                }
+                return;
+            }
             const uint32_t dst = b_base + ((BBUF == 2 ? parity : 0) * S + slot) * BT::kBytes;
             if (TM) {
                 // row n of the slice: 64 halves of token n starting at column 64 j (eight 16-byte chunks);

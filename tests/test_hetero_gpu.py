@@ -116,6 +116,35 @@ def test_integer_inputs_exact(sp, oracle, torch_cuda):
     assert np.array_equal(C.view(np.float16).astype(np.float64), want)
 
 
+def test_config_4_full_size_exact(sp, torch_cuda):
+    """BASELINE config 4 at full size (M = K = 12288, N = 32): integer weights pruned 2:4 with half of the
+    survivors zeroed, so the residual is empty and the product runs on the sparse tensor core alone; then
+    the same weights with a few third nonzeros per group put back, which go through the residual path."""
+    torch = torch_cuda
+    M = K = 12288
+    N = 32
+    rng = np.random.default_rng(13)
+    A = rng.integers(1, 3, size=(M, K)).astype(np.float16) * (rng.integers(0, 2, size=(M, K)) * 2 - 1).astype(np.float16)
+    A_bits = prune_2_of_4(A.view(np.uint16), 0.5, 17)
+    B = rng.choice(np.array([-3, -1, 1, 3], np.float16), size=(K, N))
+    Bd = torch.from_numpy(B).cuda().float()
+    A1, A2 = sp.decompose(A_bits)
+    assert not (A2 & 0x7FFF).any()
+    C = run_hetero(sp, torch, A1, None, B.view(np.uint16), M, N, K, 8).view(np.float16)
+    expect = (torch.from_numpy(A_bits.view(np.float16)).cuda().float() @ Bd).cpu().numpy()
+    assert np.abs(expect).max() < 2048
+    assert np.array_equal(C.astype(np.float32), expect)
+    # a sprinkle of extra nonzeros: groups with three or four of them feed the residual
+    extra = rng.random((M, K), dtype=np.float32) < 0.02
+    A_more = np.where(extra & (A_bits == 0), np.float16(1).view(np.uint16), A_bits).astype(np.uint16)
+    A1, A2 = sp.decompose(A_more)
+    assert (A2 & 0x7FFF).any()
+    C = run_hetero(sp, torch, A1, A2, B.view(np.uint16), M, N, K, 8).view(np.float16)
+    expect = (torch.from_numpy(A_more.view(np.float16)).cuda().float() @ Bd).cpu().numpy()
+    assert np.abs(expect).max() < 2048
+    assert np.array_equal(C.astype(np.float32), expect)
+
+
 def test_error_paths(sp, torch_cuda):
     torch = torch_cuda
     dev = torch.device("cuda:0")

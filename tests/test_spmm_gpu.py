@@ -122,6 +122,22 @@ def test_full_size_integer_inputs_are_exact(sp, torch_cuda, shape):
     assert np.array_equal(C.astype(np.float32), expect)
 
 
+def test_prefill_full_size_integer_inputs_are_exact(sp, torch_cuda):
+    """BASELINE config 3 at full size (M = K = 12288, N = 2048, eight 256-column blocks): A in {-1, 0, 1}
+    at 90 % sparsity, B in {-1, 1}; every sum is a small integer, so the fp16 result is exact."""
+    M = K = 12288
+    N = 2048
+    rng = np.random.default_rng(11)
+    A = (rng.integers(0, 2, size=(M, K)) * 2 - 1).astype(np.float16)
+    A[rng.random((M, K), dtype=np.float32) < 0.9] = 0
+    B = (rng.integers(0, 2, size=(K, N)) * 2 - 1).astype(np.float16)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    C = run_spmm(sp, torch_cuda, words, offsets, B, M, N, K, 2).view(np.float16)
+    expect = (torch_cuda.from_numpy(A).cuda().float() @ torch_cuda.from_numpy(B).cuda().float()).cpu().numpy()
+    assert np.abs(expect).max() < 2048
+    assert np.array_equal(C.astype(np.float32), expect)
+
+
 def test_linearity_at_full_size(sp, torch_cuda):
     """C(A, B1) + C(A, B2) == C(A, B1 + B2) for power-of-two scaled integer inputs (all sums exact)."""
     M, K, N = 9216, 9216, 32
