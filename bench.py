@@ -443,7 +443,7 @@ def run_prefill(args):
         tensor_peak = 1590.0
     shapes = [(12288, 12288), (49152, 12288)] if not args.small else [(12288, 12288)]
     for M, K in shapes:
-        for p in [float(x) for x in args.sweep_p.split(",")]:
+        for p in [float(x) for x in args.prefill_p.split(",")]:
             A = sp.synth_fp16((M, K), 0xA300 + int(p * 100), 0.02, p)
             words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, 64, K)
             wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
@@ -666,6 +666,7 @@ def main():
     ap.add_argument("--sweep-layers", default="qkv,out_proj,ffn1,ffn2")
     ap.add_argument("--prefill", action="store_true", help="prefill-size points (N >= 256) instead of the bench line")
     ap.add_argument("--prefill-n", default="256,512,1024,2048")
+    ap.add_argument("--prefill-p", default="0.5,0.7,0.8")
     ap.add_argument("--small", action="store_true", help="with --prefill: only the 12288 x 12288 shape")
     ap.add_argument("--row-parallel", action="store_true", help="row-parallel (by K) layer with an NCCL all-reduce, one rank per GPU")
     ap.add_argument("--hetero", action="store_true", help="heterogeneous decomposition points (structured half on the sparse tensor core)")
