@@ -31,6 +31,10 @@ struct DecodeConfig {
     static constexpr int BBUF = 1;                 // B buffers per ring slot
     static constexpr int WTMA = N == 64 ? 0 : 1;   // words staged through shared memory by bulk copy
     static constexpr int R    = D;  // staging buffers for the words: one per team (a shared ring of 9-11 measured slower)
+    // B slices (row-major layout): tiled TMA loads, issued by the MMA warps a lap ahead into a second
+    // B buffer where that fits in shared memory (N <= 16), else by the tile's decoder
+    // (N = 8 keeps the 16-byte copies: its staged rows are twice as wide as the rows of B)
+    static constexpr int BM   = N == 8 ? 0 : (N == 16 ? 2 : 1);
 };
 
 struct DeviceInfo {
@@ -150,10 +154,12 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     constexpr int NB   = N < 16 ? 16 : N;
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
+    constexpr int BM   = TM ? 0 : Cfg::BM;  // token-major B keeps the 16-byte copies
+    constexpr int BBUF = BM == 2 ? 2 : Cfg::BBUF;
     constexpr int smem =
-        decode_smem_bytes<NB, Cfg::S, Cfg::BBUF, Cfg::WTMA ? word_stage_bytes<Cfg::R, Cfg::WPT, Cfg::VPL>() : 0>();
+        decode_smem_bytes<NB, Cfg::S, BBUF, Cfg::WTMA ? word_stage_bytes<Cfg::R, Cfg::WPT, Cfg::VPL>() : 0>();
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, TM, Cfg::BBUF, Cfg::S, Cfg::WTMA, 2, Cfg::R>;
+    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, TM, BBUF, Cfg::S, Cfg::WTMA, 2, Cfg::R, BM>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
@@ -204,6 +210,42 @@ cudaError_t own_scratch_address(int device, float** out)
     return cudaSuccess;
 }
 
+
+// Describes B[K][N] (row-major halves) to the copy engine for the kernels' tiled loads of 64-row
+// slices: boxes of min(n_block, 64) columns (16 for N = 8: the columns beyond N read as zero), in the
+// swizzle mode of the staged layout.
+cudaError_t describe_b(CUtensorMap& map, const half* B, int N_Global, int K_Global, int n_block)
+{
+    using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+    static EncodeFn   encode = nullptr;
+    static std::mutex lock;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        if (encode == nullptr) {
+            void*                           fn     = nullptr;
+            cudaDriverEntryPointQueryResult status = cudaDriverEntryPointSymbolNotFound;
+            cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
+            if (e != cudaSuccess || status != cudaDriverEntryPointSuccess || fn == nullptr)
+                return e != cudaSuccess ? e : cudaErrorNotSupported;
+            encode = reinterpret_cast<EncodeFn>(fn);
+        }
+    }
+    const int                box_cols = n_block < 16 ? 16 : (n_block > 64 ? 64 : n_block);
+    const CUtensorMapSwizzle swizzle  = box_cols == 16   ? CU_TENSOR_MAP_SWIZZLE_32B
+                                        : box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B
+                                                         : CU_TENSOR_MAP_SWIZZLE_128B;
+    const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(N_Global), static_cast<cuuint64_t>(K_Global)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N_Global) * sizeof(half)};
+    const cuuint32_t box[2]     = {static_cast<cuuint32_t>(box_cols), static_cast<cuuint32_t>(kTileCols)};
+    const cuuint32_t steps[2]   = {1, 1};
+    if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(B), dims, strides, box, steps,
+               CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+        != CUDA_SUCCESS)
+        return cudaErrorInvalidValue;
+    return cudaSuccess;
+}
 
 bool aligned16(const void* p)
 {
@@ -284,29 +326,10 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.sched = cached_schedule(PlanKey{
         tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots_granted});
     params.slots_per_block_column = params.sched.slots_used;
-    if (wide && n_block >= 128) {
-        // B slices of the wide forms come by tiled TMA loads: describe B[K][N] to the copy engine
-        using EncodeFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-        static EncodeFn encode = nullptr;
-        if (encode == nullptr) {
-            void*                           fn     = nullptr;
-            cudaDriverEntryPointQueryResult status = cudaDriverEntryPointSymbolNotFound;
-            e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &status);
-            if (e != cudaSuccess || status != cudaDriverEntryPointSuccess || fn == nullptr)
-                return e != cudaSuccess ? e : cudaErrorNotSupported;
-            encode = reinterpret_cast<EncodeFn>(fn);
-        }
-        const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(N_Global), static_cast<cuuint64_t>(K_Global)};
-        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(N_Global) * sizeof(half)};
-        const cuuint32_t box[2]     = {64, static_cast<cuuint32_t>(kTileCols)};
-        const cuuint32_t steps[2]   = {1, 1};
-        if (encode(&params.b_map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(B), dims, strides, box, steps,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
-            != CUDA_SUCCESS)
-            return cudaErrorInvalidValue;
+    if (!token_major && N_Global != 8) {
+        e = describe_b(params.b_map, B, N_Global, K_Global, n_block);
+        if (e != cudaSuccess)
+            return e;
     }
     if (wide) {
         switch (n_block) {
@@ -540,6 +563,11 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
     params.m            = M_Global;
     params.ld           = N_Global;
     params.slots_per_block_column = 0;
+    if (N_Global != 8) {
+        e = describe_b(params.b_map, static_cast<const half*>(B), N_Global, K_Global, N_Global);
+        if (e != cudaSuccess)
+            return static_cast<int>(e);
+    }
     params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, static_cast<long>(kOwnScratchBytes / slot_bytes)});
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (N_Global) {

@@ -182,6 +182,10 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 //       team that has just emptied a buffer (tile l) asks for tile l + R into it, so R tiles are in
 //       flight per block whichever team will consume them.  The copy of a tile is then issued R
 //       tiles, not one round of D tiles, before it is needed.
+// BM  : how a tile's B slice reaches shared memory.  0: 16-byte async copies by the decoders;
+//       1: tiled TMA loads issued by the tile's decoder after the slot has been handed back;
+//       2: tiled TMA loads issued by the MMA warp one lap ahead into the other of two B buffers
+//       (the decoders never touch B; needs BBUF == 2).  1 and 2 need p.b_map and row-major B.
 // BBUF : B buffers per slot.  2: the next tile's slice is fetched while this one is decoded (needs
 //       S == D); 1: the slice is fetched after the slot has been handed back.
 // ABL : debugging ablation mask (0 in production): 1 no clearing, 2 no scatter, 4 no word loads,
@@ -189,7 +193,7 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
 // TM : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
 //      library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
 //      k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TM = 0, int BBUF = 2, int S_ = 0, int WTMA = 0, int PFR = 2, int R_ = 0>
+template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TM = 0, int BBUF = 2, int S_ = 0, int WTMA = 0, int PFR = 2, int R_ = 0, int BM = 0>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
@@ -290,13 +294,15 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // B staging: a 64 x N slice is kTileCols * N / 8 chunks of 16 bytes, contiguous in global
         // memory; this warp copies chunks first_chunk, first_chunk + WPT * 32, ...  Chunk c lands at
         // swizzle(row * row_bytes + col * 16) with row = c / chunks_per_row, col = c % chunks_per_row.
-        constexpr bool kBTma        = N >= 128 && !TM;
-        static_assert(!kBTma || BBUF == 1, "tiled loads of B go to the slot's only B buffer");
+        constexpr bool kBTma        = BM == 1;
+        static_assert(!kBTma || BBUF == 1, "tiled loads of B by the decoder go to the slot's only B buffer");
+        static_assert(BM == 0 || !TM, "tiled loads of B are for the row-major layout");
+        static_assert(BM != 2 || (BBUF == 2 && Q > 0), "loads of B issued by the MMA warps use two B buffers");
         constexpr int kChunksPerRow = N / 8;
         constexpr int kChunks       = kTileCols * kChunksPerRow;
         const int     first_chunk   = h * 32 + lane;
         auto stage_b = [&](int j, int parity) {
-            if (ABL & 16)
+            if ((ABL & 16) || BM == 2)
                 return;
             if (kBTma) {
                 // one box of 64 k rows x 64 columns per swizzle atom; the bytes are counted on the
@@ -307,7 +313,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 #pragma unroll
                     for (int a = 0; a < BT::kAtoms; a++)
                         ptx::tma_load_2d(b_base + slot * BT::kBytes + a * BT::kAtomBytes, &p.b_map,
-                                         static_cast<int>(blockIdx.y) * N + a * 64, j * kTileCols, bar);
+                                         static_cast<int>(blockIdx.y) * N + a * BT::kAtomCols, j * kTileCols, bar);
                 }
                 return;
             }
@@ -599,6 +605,25 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const uint64_t     b_desc0 =
                 TM ? ptx::make_smem_desc(b_base, 16, 1024, ptx::kSwizzle128B)
                    : ptx::make_smem_desc(b_base, BT::kLeadingBytes, BT::kGroupBytes, BT::kSwizzleMode);
+            // BM == 2: the B slice of chunk-local tile l goes to buffer (l / S) % 2 of slot l % S and is
+            // counted on that slot's tile_full barrier, which is in the phase of tile l once the fill of
+            // tile l - S has completed (or from the start, for the first lap).
+            auto load_b = [&](int l) {
+                const int      s   = l % S;
+                const uint32_t bar = tile_full(s);
+                const uint32_t dst = b_base + ((((l / S) & 1) * S) + s) * BT::kBytes;
+                const int      j   = (tile_begin + l) % tiles_k;
+                ptx::mbar_expect_tx(bar, BT::kBytes);
+#pragma unroll
+                for (int a = 0; a < BT::kAtoms; a++)
+                    ptx::tma_load_2d(dst + a * BT::kAtomBytes, &p.b_map, static_cast<int>(blockIdx.y) * N + a * BT::kAtomCols,
+                                     j * kTileCols, bar);
+            };
+            if (BM == 2) {
+#pragma unroll 1
+                for (int l = q; l < S && l < num_tiles; l += Q)
+                    load_b(l);
+            }
             bool ok  = true;
             int  seg = 0;
 #pragma unroll 1
@@ -631,6 +656,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     }
                     ptx::umma_commit(tile_free(s));
                     accumulate = 1;
+                    if (BM == 2 && l + S < num_tiles)
+                        load_b(l + S);
                 }
                 if (ok) {
                     if (first < l0 + len)
