@@ -13,6 +13,13 @@
 #include "spmm_decode_kernel.cuh"
 #include "spmm_structured_kernel.cuh"
 
+#ifndef SPMM_B200_PFR
+#define SPMM_B200_PFR 2  // rounds ahead at which a team asks for its words to be brought into L2 (0 = never)
+#endif
+#ifndef SPMM_B200_ABL
+#define SPMM_B200_ABL 0  // experiment builds: ablation mask of spmm_decode_kernel (see its template parameters)
+#endif
+
 namespace spmm_b200 {
 namespace {
 
@@ -80,77 +87,10 @@ const Schedule& cached_schedule(const PlanKey& key)
     return plans[slot];
 }
 
-#ifdef SPMM_B200_ABLATIONS
-// Experiment builds only: ring shapes and ablation masks chosen through the environment (N = 16).
-template<int D, int Q, int S, int BBUF, int WTMA, int ABL>
-cudaError_t launch_ablated(cudaStream_t stream, const DecodeParams& params)
-{
-    constexpr int smem = decode_smem_bytes<16, S, BBUF, WTMA ? word_stage_bytes<D, 1, 14>() : 0>();
-    const char*   envp = getenv("SPMM_B200_PFR");
-    const int     pfr  = envp ? atoi(envp) : 2;
-    auto          kern = pfr == 4 ? spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 4>
-                       : pfr == 8 ? spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 8>
-                       : pfr == 1 ? spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 1>
-                                  : spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, BBUF, S, WTMA, 2>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    if (const char* envs = getenv("SPMM_B200_CARVEOUT"))
-        cudaFuncSetAttribute(kern, cudaFuncAttributePreferredSharedMemoryCarveout, atoi(envs));
-    kern<<<params.sched.num_ctas, decode_threads<D, Q, 1>(), smem, stream>>>(params);
-    return cudaGetLastError();
-}
-template<int R, int PFR = 2, int ABL = 0>
-cudaError_t launch_staging_ring(cudaStream_t stream, const DecodeParams& params)
-{
-    constexpr int D = 8, Q = 4;
-    constexpr int smem = decode_smem_bytes<16, D, 1, word_stage_bytes<R, 1, 14>()>();
-    auto          kern = spmm_decode_kernel<16, D, Q, 1, 14, ABL, 0, 1, D, 1, PFR, R>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    kern<<<params.sched.num_ctas, decode_threads<D, Q, 1>(), smem, stream>>>(params);
-    return cudaGetLastError();
-}
-template<int D, int Q>
-cudaError_t launch_two_warp_teams(cudaStream_t stream, const DecodeParams& params)
-{
-    constexpr int smem = decode_smem_bytes<16, D, 1, word_stage_bytes<D, 2, 7>()>();
-    auto          kern = spmm_decode_kernel<16, D, Q, 2, 7, 0, 0, 1, D, 1>;
-    cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-    kern<<<params.sched.num_ctas, decode_threads<D, Q, 2>(), smem, stream>>>(params);
-    return cudaGetLastError();
-}
-template<int D, int Q, int S, int BBUF, int WTMA>
-cudaError_t launch_ablated_d(cudaStream_t stream, const DecodeParams& params, int abl)
-{
-    switch (abl) {
-        case 3: return launch_ablated<D, Q, S, BBUF, WTMA, 3>(stream, params);
-        default: return launch_ablated<D, Q, S, BBUF, WTMA, 0>(stream, params);
-    }
-}
-#endif
-
 template<int N, int TM = 0>
 cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, const DecodeParams& params,
                           int column_blocks = 1)
 {
-#ifdef SPMM_B200_ABLATIONS
-    if (N == 16 && !TM) {
-        const char* env  = getenv("SPMM_B200_ABLATE");
-        const char* envc = getenv("SPMM_B200_CFG");
-        const int   abl  = env ? atoi(env) : 0;
-        switch (envc ? atoi(envc) : 0) {
-            case 1: return launch_ablated_d<8, 4, 8, 2, 0>(stream, params, abl);
-            case 3: return launch_ablated_d<8, 4, 8, 1, 1>(stream, params, abl);
-            case 4: return launch_staging_ring<11, 1>(stream, params);
-            case 5: return launch_staging_ring<11, 3>(stream, params);
-            case 6: return launch_staging_ring<11, 4>(stream, params);
-            case 7: return launch_staging_ring<11, 3, 3>(stream, params);
-            case 8: return launch_staging_ring<8, 2, 3>(stream, params);
-            case 9: return launch_staging_ring<8, 0>(stream, params);
-            case 10: return launch_staging_ring<11, 0>(stream, params);
-            case 11: return launch_staging_ring<8, 0, 3>(stream, params);
-            default: break;
-        }
-    }
-#endif
     constexpr int NB   = N < 16 ? 16 : N;
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
@@ -159,7 +99,7 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     constexpr int smem =
         decode_smem_bytes<NB, Cfg::S, BBUF, Cfg::WTMA ? word_stage_bytes<Cfg::R, Cfg::WPT, Cfg::VPL>() : 0>();
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, 0, TM, BBUF, Cfg::S, Cfg::WTMA, 2, Cfg::R, BM>;
+    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, SPMM_B200_ABL, TM, BBUF, Cfg::S, Cfg::WTMA, SPMM_B200_PFR, Cfg::R, BM>;
     if (!dev.attrs_set[n_index]) {
         cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) {
