@@ -535,6 +535,21 @@ def run_row_parallel(args):
 
     ms_spmm = timed(spmm_only) / 2
     ms_full = timed(with_reduce) / 2
+    # the same with the library's own reduction kernel over peer memory instead of NCCL
+    ms_peer = None
+    if world > 1:
+        try:
+            peer_layers = [RowParallelSpMM(l.words, l.offsets, M, N, K_shard, split_k=8, reduce="peer") for l in (layer, other)]
+
+            def with_peer_reduce():
+                for l in peer_layers:
+                    l.forward(Bd)
+
+            ms_peer = timed(with_peer_reduce) / 2
+            assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
+        except Exception as exc:  # symmetric memory not available on this box
+            if rank == 0:
+                print("peer-memory reduction unavailable:", exc, file=sys.stderr)
     assert sp.device_status() == 0
     if rank == 0:
         peak, src = measured_hbm_peak()
@@ -543,6 +558,7 @@ def run_row_parallel(args):
             "value": round(world * wbytes / (ms_full * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
             "steps": args.steps, "warmup": max(args.warmup, 3), "scaling": "weak", "higher_is_better": True,
             "spmm_only_us": round(ms_spmm * 1e3, 2), "spmm_plus_allreduce_us": round(ms_full * 1e3, 2),
+            "spmm_plus_peer_reduce_us": round(ms_peer * 1e3, 2) if ms_peer else None,
             "spmm_only_gbs_per_gpu": round(wbytes / (ms_spmm * 1e-3) / 1e9, 1),
             "allreduce_bytes": M * N * 2,
             "config": {"workload": "row_parallel_ffn2", "M": M, "K_per_rank": K_shard, "n_tokens": N, "sparsity": SPARSITY,

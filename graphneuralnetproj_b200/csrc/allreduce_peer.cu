@@ -1,0 +1,155 @@
+// Sum of the ranks' partial results of a row-parallel (split by K) SpMM, read straight out of the
+// peers' memory over NVLink: one kernel per rank, no library collective.
+//
+// The reference is single-GPU; its weight-conversion tool splits out-proj and FFN2 by K
+// (end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:134-135) and leaves the sum to
+// FasterTransformer's NCCL all-reduce.  For the 0.3 MB results of decode-size layers that all-reduce
+// is latency-bound (15-30 us against a 76 us SpMM); here every rank
+//   1. tells every peer that its partial result is complete (one 32-bit flag per peer, written into
+//      the peer's memory after a system-scope fence),
+//   2. waits until all peers have told it the same (bounded spin on its own flags),
+//   3. adds the g partial results element by element in rank order (16-byte loads from the peers'
+//      buffers, fp32 sums, one rounding) and writes the sum to a local output.
+// Flags carry the call's epoch, which only grows, so nothing is reset; the callers alternate between
+// two result buffers, so a fast rank's next SpMM never overwrites what a slow peer is still reading
+// (a rank reaches the flag exchange of call n + 1 only after its reads of call n have finished).
+//
+// The buffers and flag arrays are symmetric allocations mapped into every rank's address space by
+// the caller (torch.distributed._symmetric_memory in the Python mirror); this file only takes
+// pointers.  One process per GPU; the ranks must not share a GPU (each waits for the others).
+#include <cstdint>
+
+#include <cuda_fp16.h>
+#include <cuda_runtime.h>
+
+#include "../../include/spmm_b200.h"
+#include "ptx_sm100.cuh"
+
+namespace spmm_b200 {
+
+__device__ int g_device_status_allreduce;  // 1 after a wait for the peers ran out
+
+constexpr int kMaxRanks = 16;
+
+struct AllReduceParams {
+    const uint4* partial[kMaxRanks];  // every rank's partial result, count halves each
+    uint32_t*    flags[kMaxRanks];    // flags[p] = rank p's flag array (world entries, one per sender)
+    uint4*       out;                 // local result
+    size_t       vectors;             // count / 8
+    int          rank, world;
+    uint32_t     epoch;
+    unsigned long long limit_ns;
+};
+
+__global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_constant__ AllReduceParams p)
+{
+    __shared__ int ok;
+    ptx::grid_dependency_wait();  // the SpMM before this kernel in the stream wrote this rank's partial result
+    if (threadIdx.x == 0)
+        ok = 1;
+    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+        // this rank's partial result is complete and visible: tell peer threadIdx.x
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.rank), "r"(p.epoch) : "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x < p.world) {
+        const uint32_t*          mine  = p.flags[p.rank] + threadIdx.x;
+        const unsigned long long start = ptx::global_timer_ns();
+        for (unsigned polls = 0;; polls++) {
+            uint32_t seen;
+            asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+            if (static_cast<int32_t>(seen - p.epoch) >= 0)
+                break;
+            if ((polls & 255u) == 255u && ptx::global_timer_ns() - start > p.limit_ns) {
+                ok = 0;  // a peer never arrived: give up, report, leave the output untouched
+                atomicExch(&g_device_status_allreduce, 1);
+                break;
+            }
+        }
+    }
+    __syncthreads();
+    if (!ok)
+        return;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.vectors;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+        for (int r = 0; r < p.world; r++) {
+            const uint4    v = __ldcv(p.partial[r] + i);  // peer memory, rewritten every other call: never from a cache
+            const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+            for (int k = 0; k < 4; k++) {
+                const float2 f = __half22float2(h[k]);
+                sum[2 * k] += f.x;
+                sum[2 * k + 1] += f.y;
+            }
+        }
+        uint4    o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            oh[k] = __floats2half2_rn(sum[2 * k], sum[2 * k + 1]);
+        p.out[i] = o;
+    }
+}
+
+}  // namespace spmm_b200
+
+extern "C" int spmm_b200_allreduce_partials(void*              stream,
+                                            const void* const* partial_buffers,
+                                            void* const*       flag_arrays,
+                                            int                rank,
+                                            int                world,
+                                            void*              out,
+                                            size_t             count,
+                                            uint32_t           epoch,
+                                            unsigned           limit_ms)
+{
+    using namespace spmm_b200;
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || count % 8 != 0 || !out || !partial_buffers
+        || !flag_arrays || epoch == 0)
+        return static_cast<int>(cudaErrorInvalidValue);
+    AllReduceParams p;
+    for (int r = 0; r < world; r++) {
+        if (!partial_buffers[r] || !flag_arrays[r] || (reinterpret_cast<uintptr_t>(partial_buffers[r]) & 15u))
+            return static_cast<int>(cudaErrorInvalidValue);
+        p.partial[r] = static_cast<const uint4*>(partial_buffers[r]);
+        p.flags[r]   = static_cast<uint32_t*>(flag_arrays[r]);
+    }
+    if (reinterpret_cast<uintptr_t>(out) & 15u)
+        return static_cast<int>(cudaErrorInvalidValue);
+    p.out      = static_cast<uint4*>(out);
+    p.vectors  = count / 8;
+    p.rank     = rank;
+    p.world    = world;
+    p.epoch    = epoch;
+    p.limit_ns = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
+    const int blocks = static_cast<int>(p.vectors < 256 * 148 ? (p.vectors + 255) / 256 : 148);
+    cudaLaunchConfig_t config = {};
+    config.gridDim            = dim3(blocks > 0 ? blocks : 1);
+    config.blockDim           = dim3(256);
+    config.stream             = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                       = attr;
+    config.numAttrs                                    = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, allreduce_partials_kernel, p);
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+
+extern "C" int spmm_b200_allreduce_status(int reset)
+{
+    int         status = 0;
+    cudaError_t e      = cudaDeviceSynchronize();
+    if (e != cudaSuccess)
+        return -static_cast<int>(e);
+    e = cudaMemcpyFromSymbol(&status, spmm_b200::g_device_status_allreduce, sizeof(int));
+    if (e != cudaSuccess)
+        return -static_cast<int>(e);
+    if (reset) {
+        const int zero = 0;
+        cudaMemcpyToSymbol(spmm_b200::g_device_status_allreduce, &zero, sizeof(int));
+    }
+    return status;
+}

@@ -50,6 +50,12 @@ def _load():
     lib.spmm_b200_pack_a1.argtypes = [_u16p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(ctypes.c_void_p),
                                       ctypes.POINTER(ctypes.c_void_p)]
     lib.spmm_b200_pack_a1.restype = ctypes.c_int
+    lib.spmm_b200_allreduce_partials.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                                 ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32,
+                                                 ctypes.c_uint]
+    lib.spmm_b200_allreduce_partials.restype = ctypes.c_int
+    lib.spmm_b200_allreduce_status.argtypes = [ctypes.c_int]
+    lib.spmm_b200_allreduce_status.restype = ctypes.c_int
     lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
     for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):

@@ -60,10 +60,70 @@ def all_reduce_partial(C_partial, group=None):
     return C_partial
 
 
-class RowParallelSpMM:
-    """One rank's part of a row-parallel layer on its GPU: SpMM over its K shard, then the all-reduce."""
+class PeerAllReduce:
+    """Sum of the ranks' fp16 partial results by the library's own kernel, which reads the peers'
+    buffers over NVLink (csrc/allreduce_peer.cu) instead of calling a collective library.
 
-    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8):
+    Holds two symmetric result buffers per rank (the SpMM of call n writes into `next_buffer()`, the
+    kernel of call n reads all ranks' copies of it) and one symmetric flag array.  Every rank must
+    construct it and call `reduce` the same number of times.  One process per GPU."""
+
+    def __init__(self, count, device, group=None):
+        import ctypes
+        import os
+
+        # plain peer mappings only: no NVLink multicast object is bound to these buffers
+        os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")
+        import torch
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm_mem
+
+        from . import spmm_api
+        self._api = spmm_api
+        group = group if group is not None else dist.group.WORLD
+        self.rank, self.world = dist.get_rank(group), dist.get_world_size(group)
+        if count % 8:
+            raise ValueError("count must be a multiple of 8 halves")
+        self.count = count
+        self.buffers = [symm_mem.empty(count, dtype=torch.float16, device=device) for _ in range(2)]
+        self.flags = symm_mem.empty(64, dtype=torch.int32, device=device)
+        self.flags.zero_()
+        handles = [symm_mem.rendezvous(b, group) for b in self.buffers]
+        flag_handle = symm_mem.rendezvous(self.flags, group)
+        self._handles = handles + [flag_handle]  # keep the mappings alive
+        ptr_array = ctypes.c_void_p * self.world
+        self._buffer_ptrs = [ptr_array(*[int(p) for p in h.buffer_ptrs]) for h in handles]
+        self._flag_ptrs = ptr_array(*[int(p) for p in flag_handle.buffer_ptrs])
+        self.out = torch.empty(count, dtype=torch.float16, device=device)
+        self.epoch = 0
+        torch.cuda.synchronize(device)
+        dist.barrier(group)  # nobody signals before every flag array is zero
+
+    def next_buffer(self):
+        """Where this rank's next partial result belongs (a view of the symmetric buffer)."""
+        return self.buffers[(self.epoch + 1) & 1]
+
+    def reduce(self, stream=None, limit_ms=2000):
+        """Sums the partial results written into `next_buffer()` on every rank; returns the local sum."""
+        import ctypes
+
+        import torch
+        if stream is None:
+            stream = torch.cuda.current_stream()
+        self.epoch += 1
+        rc = self._api.LIB.spmm_b200_allreduce_partials(ctypes.c_void_p(stream.cuda_stream), self._buffer_ptrs[self.epoch & 1],
+                                                        self._flag_ptrs, self.rank, self.world,
+                                                        ctypes.c_void_p(self.out.data_ptr()), self.count, self.epoch, limit_ms)
+        if rc != 0:
+            raise RuntimeError("spmm_b200_allreduce_partials failed with cudaError %d" % rc)
+        return self.out
+
+
+class RowParallelSpMM:
+    """One rank's part of a row-parallel layer on its GPU: SpMM over its K shard, then the sum over ranks,
+    by NCCL (`reduce="nccl"`) or by the library's own peer-memory kernel (`reduce="peer"`)."""
+
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, reduce="nccl", group=None):
         import torch
         from . import spmm_api
         self._api = spmm_api
@@ -73,10 +133,14 @@ class RowParallelSpMM:
         dev = words_dev.device
         self.C = torch.zeros((M, N), dtype=torch.float16, device=dev)
         self.workspace = torch.zeros(spmm_api.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
+        self.peer = PeerAllReduce(M * N, dev, group) if reduce == "peer" else None
 
     def forward(self, B_shard_dev, group=None):
-        rc = self._api.SpMM_SplitK_API(None, None, self.words, None, None, self.offsets, B_shard_dev, self.C, self.M,
+        C = self.peer.next_buffer() if self.peer is not None else self.C
+        rc = self._api.SpMM_SplitK_API(None, None, self.words, None, None, self.offsets, B_shard_dev, C, self.M,
                                        self.N, self.K, self.workspace, self.split_k)
         if rc != 0:
             raise RuntimeError("SpMM_SplitK_API failed with cudaError %d" % rc)
+        if self.peer is not None:
+            return self.peer.reduce().view(self.M, self.N)
         return all_reduce_partial(self.C, group)

@@ -106,6 +106,27 @@ int spmm_b200_spmm_own_scratch(void*       stream,
                                int         N_Global,
                                int         K_Global);
 
+/* Sum of the partial results of a row-parallel (split by K) layer, read out of the peers' memory over
+ * NVLink by one kernel per rank; no counterpart in the reference (single-GPU; its FasterTransformer
+ * glue all-reduces with NCCL).  partial_buffers[r] / flag_arrays[r]: rank r's partial result (count
+ * halves, 16-byte aligned) and flag array (at least `world` 32-bit words, zero before the first
+ * call), both mapped into this process (symmetric memory); host arrays of `world` device pointers.
+ * out: local result, count halves.  epoch: 1, 2, 3, ... the same on every rank for the same call;
+ * callers alternate between two sets of partial buffers from call to call.  Every rank must make
+ * the matching call; a rank whose peers do not arrive within limit_ms (0 = 2000) leaves `out`
+ * untouched and raises the status read by spmm_b200_allreduce_status.  One process per GPU. */
+int spmm_b200_allreduce_partials(void*              stream,
+                                 const void* const* partial_buffers,
+                                 void* const*       flag_arrays,
+                                 int                rank,
+                                 int                world,
+                                 void*              out,
+                                 size_t             count,
+                                 uint32_t           epoch,
+                                 unsigned           limit_ms);
+/* 0, or 1 if a wait inside spmm_b200_allreduce_partials ran out (synchronises the device). */
+int spmm_b200_allreduce_status(int reset);
+
 /* The reference's workspace contract, build/SpMM_API.cuh:34-38:
  * Split_K * M * N * sizeof(half) bytes. */
 size_t spmm_b200_workspace_bytes(int M_Global, int N_Global, int Split_K);

@@ -73,10 +73,19 @@ else:
     if backend == "nccl":
         dev = torch.device("cuda", rank)
         layer = tp.RowParallelSpMM(torch.from_numpy(np.concatenate([w, np.zeros(4, np.uint32)]).view(np.int32)).to(dev),
-                                   torch.from_numpy(o).to(dev), M, N, k)
-        C = layer.forward(torch.from_numpy(Bs.view(np.int16)).to(dev))
+                                   torch.from_numpy(o).to(dev), M, N, k, reduce="peer" if mode == "row_peer" else "nccl")
+        Bd = torch.from_numpy(Bs.view(np.int16)).to(dev)
+        C = layer.forward(Bd)
         torch.cuda.synchronize(); assert sp.device_status() == 0
         total = C.cpu().numpy().view(np.uint16)
+        if mode == "row_peer":
+            # the library's own reduction over peer memory: several calls in a row (the two result buffers
+            # alternate), each with the same answer, and the wait for the peers never ran out
+            for _ in range(5):
+                again = layer.forward(Bd)
+            torch.cuda.synchronize()
+            assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
+            assert np.array_equal(again.cpu().numpy().view(np.uint16), total)
     else:
         part = torch.from_numpy(oracle.spmm_from_csl(w, o, Bs, M, k).view(np.float16).astype(np.float32))
         total = tp.all_reduce_partial(part).numpy().astype(np.float16).view(np.uint16)
@@ -109,7 +118,7 @@ def test_two_gloo_ranks_on_cpu(mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["column", "row"])
+@pytest.mark.parametrize("mode", ["column", "row", "row_peer"])
 def test_two_nccl_ranks_on_gpus(mode):
     import torch
     if torch.cuda.device_count() < 2:
