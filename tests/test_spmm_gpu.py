@@ -222,6 +222,33 @@ def test_wide_n_in_column_blocks(sp, oracle, torch_cuda, case):
     assert np.abs(a - b).max() <= 2e-3 * np.abs(b).max()
 
 
+def test_peer_reduction_gives_up_when_a_peer_never_arrives(sp, torch_cuda):
+    """Failure detection without a fault, for the row-parallel reduction kernel: rank 0 of a world of two whose
+    peer never signals.  The bounded wait runs out after 50 ms, the kernel returns, the output is untouched,
+    the status says so, and with both flags set the same call then sums the two buffers."""
+    import ctypes
+    torch = torch_cuda
+    dev = torch.device("cuda:0")
+    lib = sp.spmm_api.LIB
+    count = 4096
+    mine = torch.full((count,), 1.5, dtype=torch.float16, device=dev)
+    theirs = torch.full((count,), 2.25, dtype=torch.float16, device=dev)
+    flags = [torch.zeros(64, dtype=torch.int32, device=dev) for _ in range(2)]
+    out = torch.full((count,), -1.0, dtype=torch.float16, device=dev)
+    ptrs = (ctypes.c_void_p * 2)(mine.data_ptr(), theirs.data_ptr())
+    fptrs = (ctypes.c_void_p * 2)(flags[0].data_ptr(), flags[1].data_ptr())
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+    assert lib.spmm_b200_allreduce_status(1) >= 0
+    assert lib.spmm_b200_allreduce_partials(stream, ptrs, fptrs, 0, 2, ctypes.c_void_p(out.data_ptr()), count, 1, 50) == 0
+    assert lib.spmm_b200_allreduce_status(1) == 1
+    assert bool((out == -1.0).all())
+    flags[0][1] = 2  # what the peer would have written for epoch 2
+    torch.cuda.synchronize()
+    assert lib.spmm_b200_allreduce_partials(stream, ptrs, fptrs, 0, 2, ctypes.c_void_p(out.data_ptr()), count, 2, 50) == 0
+    assert lib.spmm_b200_allreduce_status(0) == 0
+    assert bool((out == 3.75).all())
+
+
 def test_host_buffer_entry_point(sp, oracle, torch_cuda):
     """The C call that takes B and C in page-locked host memory gives the result of the device-pointer call."""
     torch = torch_cuda
