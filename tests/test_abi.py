@@ -58,3 +58,18 @@ def test_reference_symbol_names_match(oracle):
 
 def test_workspace_contract(sp):
     assert sp.workspace_bytes(7168, 16, 5) == 5 * 7168 * 16 * 2
+
+
+def test_argument_checks_need_no_gpu(sp):
+    """Entry points reject bad arguments before any CUDA call (cudaErrorInvalidValue = 1)."""
+    import ctypes
+    lib = sp.spmm_api.LIB
+    # host-buffer SpMM: missing buffers
+    assert lib.spmm_b200_spmm_splitk_host_io(None, None, None, None, None, None, None, 128, 16, 64, None, 1) == 1
+    # peer reduction: world out of range, count not a multiple of eight halves, epoch 0, null tables
+    two = (ctypes.c_void_p * 2)(16, 32)
+    assert lib.spmm_b200_allreduce_partials(None, two, two, 0, 0, ctypes.c_void_p(16), 64, 1, 0) == 1
+    assert lib.spmm_b200_allreduce_partials(None, two, two, 0, 2, ctypes.c_void_p(16), 60, 1, 0) == 1
+    assert lib.spmm_b200_allreduce_partials(None, two, two, 0, 2, ctypes.c_void_p(16), 64, 0, 0) == 1
+    assert lib.spmm_b200_allreduce_partials(None, None, two, 0, 2, ctypes.c_void_p(16), 64, 1, 0) == 1
+    assert lib.spmm_b200_allreduce_partials(None, two, two, 2, 2, ctypes.c_void_p(16), 64, 1, 0) == 1
