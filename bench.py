@@ -593,7 +593,7 @@ def run_hetero(args):
     torch.cuda.set_device(0)
     peak, _ = measured_hbm_peak()
     M = K = args.hetero_size
-    N = 32
+    N = args.hetero_n
 
     def timed(fn, copies):
         for i in range(3):
@@ -688,6 +688,7 @@ def main():
     ap.add_argument("--row-parallel", action="store_true", help="row-parallel (by K) layer with an NCCL all-reduce, one rank per GPU")
     ap.add_argument("--hetero", action="store_true", help="heterogeneous decomposition points (structured half on the sparse tensor core)")
     ap.add_argument("--hetero-size", type=int, default=12288)
+    ap.add_argument("--hetero-n", type=int, default=32)
     args = ap.parse_args()
     if args.row_parallel:
         run_row_parallel(args)
