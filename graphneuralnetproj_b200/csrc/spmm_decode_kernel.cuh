@@ -404,7 +404,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         int  after0 = 0, after1 = 0, pf0 = 0, pf1 = 0;
         int  ring0 = 0, ring1 = 0;  // offsets of tile l + R, read one iteration before they are used
         auto prefetch_tile = [&](int off0, int off1) {
-            if (PFR > 0 && h == 0 && lane == 0 && off1 > off0)
+            // (with BM == 2 the MMA warps make these requests, as they make the loads of B)
+            if (PFR > 0 && BM != 2 && h == 0 && lane == 0 && off1 > off0)
                 ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
         };
         if (s_own < num_tiles) {
@@ -619,10 +620,20 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     ptx::tma_load_2d(dst + a * BT::kAtomBytes, &p.b_map, static_cast<int>(blockIdx.y) * N + a * BT::kAtomCols,
                                      j * kTileCols, bar);
             };
+            // BM == 2: this lane also asks for the words of its tiles PFR laps ahead to be brought into L2
+            auto request_words = [&](int off0, int off1) {
+                if (off1 > off0)
+                    ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
+            };
             if (BM == 2) {
 #pragma unroll 1
                 for (int l = q; l < S && l < num_tiles; l += Q)
                     load_b(l);
+                if (PFR > 0) {
+#pragma unroll 1
+                    for (int l = q + S; l < PFR * S && l < num_tiles; l += Q)
+                        request_words(__ldg(p.tile_offsets + tile_begin + l), __ldg(p.tile_offsets + tile_begin + l + 1));
+                }
             }
             bool ok  = true;
             int  seg = 0;
@@ -639,6 +650,11 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 for (int l = first; l < l0 + len && ok; l += Q) {
                     const int      s      = l % S;
                     const uint32_t parity = (l / S) & 1;
+                    int            ahead0 = 0, ahead1 = 0;  // offsets of tile l + PFR * S, read while waiting
+                    if (BM == 2 && PFR > 0 && l + PFR * S < num_tiles) {
+                        ahead0 = __ldg(p.tile_offsets + tile_begin + l + PFR * S);
+                        ahead1 = __ldg(p.tile_offsets + tile_begin + l + PFR * S + 1);
+                    }
                     ok = ptx::mbar_wait_bounded(tile_full(s), parity, abort_word);
                     if (!ok)
                         break;
@@ -658,6 +674,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     accumulate = 1;
                     if (BM == 2 && l + S < num_tiles)
                         load_b(l + S);
+                    if (BM == 2)
+                        request_words(ahead0, ahead1);
                 }
                 if (ok) {
                     if (first < l0 + len)
