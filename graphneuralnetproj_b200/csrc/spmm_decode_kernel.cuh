@@ -233,6 +233,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const int num_tiles  = tile_end - tile_begin;
     const int tiles_k    = p.tiles_k;
     constexpr int      kFirstDecodeWarp = kFirstMmaWarp + Q;
+    // Who asks for the words PFR laps ahead to be brought into L2: the MMA warps (which have time to
+    // spare) wherever the kernel uses the tensor-map forms of loading B, else the decoders.
+    constexpr bool     kMmaRequests     = BM != 0;
     constexpr uint32_t kTmemCols        = tmem_columns(2 * Q * NB);  // accumulator (q, b) at column (b * Q + q) * NB
     static_assert(2 * Q * NB <= 512, "accumulators exceed the 512 TMEM columns");
     static_assert(S % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
@@ -404,8 +407,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         int  after0 = 0, after1 = 0, pf0 = 0, pf1 = 0;
         int  ring0 = 0, ring1 = 0;  // offsets of tile l + R, read one iteration before they are used
         auto prefetch_tile = [&](int off0, int off1) {
-            // (with BM == 2 the MMA warps make these requests, as they make the loads of B)
-            if (PFR > 0 && BM != 2 && h == 0 && lane == 0 && off1 > off0)
+            if (PFR > 0 && !kMmaRequests && h == 0 && lane == 0 && off1 > off0)
                 ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
         };
         if (s_own < num_tiles) {
@@ -620,7 +622,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     ptx::tma_load_2d(dst + a * BT::kAtomBytes, &p.b_map, static_cast<int>(blockIdx.y) * N + a * BT::kAtomCols,
                                      j * kTileCols, bar);
             };
-            // BM == 2: this lane also asks for the words of its tiles PFR laps ahead to be brought into L2
+            // kMmaRequests: this lane also asks for the words of its tiles PFR laps ahead to be brought into L2
             auto request_words = [&](int off0, int off1) {
                 if (off1 > off0)
                     ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
@@ -629,11 +631,11 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 #pragma unroll 1
                 for (int l = q; l < S && l < num_tiles; l += Q)
                     load_b(l);
-                if (PFR > 0) {
+            }
+            if (kMmaRequests && PFR > 0) {
 #pragma unroll 1
-                    for (int l = q + S; l < PFR * S && l < num_tiles; l += Q)
-                        request_words(__ldg(p.tile_offsets + tile_begin + l), __ldg(p.tile_offsets + tile_begin + l + 1));
-                }
+                for (int l = q + S; l < PFR * S && l < num_tiles; l += Q)
+                    request_words(__ldg(p.tile_offsets + tile_begin + l), __ldg(p.tile_offsets + tile_begin + l + 1));
             }
             bool ok  = true;
             int  seg = 0;
@@ -651,7 +653,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     const int      s      = l % S;
                     const uint32_t parity = (l / S) & 1;
                     int            ahead0 = 0, ahead1 = 0;  // offsets of tile l + PFR * S, read while waiting
-                    if (BM == 2 && PFR > 0 && l + PFR * S < num_tiles) {
+                    if (kMmaRequests && PFR > 0 && l + PFR * S < num_tiles) {
                         ahead0 = __ldg(p.tile_offsets + tile_begin + l + PFR * S);
                         ahead1 = __ldg(p.tile_offsets + tile_begin + l + PFR * S + 1);
                     }
@@ -674,7 +676,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     accumulate = 1;
                     if (BM == 2 && l + S < num_tiles)
                         load_b(l + S);
-                    if (BM == 2)
+                    if (kMmaRequests)
                         request_words(ahead0, ahead1);
                 }
                 if (ok) {
