@@ -8,10 +8,14 @@ the library's InitSparseMatrixA_API and resident in HBM before the timed region.
 
     python bench.py --gpus N --steps K --warmup W [--impl reference]
 
-Prints one JSON line (rank 0).  `value` is effective weight-HBM GB/s, (4*NNZ_pad +
-4*NumOffsets) summed over the step and all ranks, divided by the device time (max over
-ranks).  With N > 1 every rank runs the same per-GPU workload on its own row shard of an
-N-times taller, column-parallel layer: no collective on the data path, weak scaling.
+Prints one JSON line (rank 0).  `value` is effective weight-HBM GB/s: (4*NNZ_pad + 4*NumOffsets)
+summed over the step and all ranks, divided by the device time of a step (max over ranks).
+
+With N > 1 the SAME block is sharded tensor-parallel the way the reference's conversion tool shards
+it (end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:134-135): QKV and FFN1 by output
+rows (no collective), out-proj and FFN2 by K with the sum over ranks inside the timed step (strong
+scaling).  Every rank draws only its own shard of the seeded matrix, which is bit-identical to
+cutting the shard out of the whole matrix.
 """
 import argparse
 import json
@@ -26,28 +30,37 @@ ROOT = os.path.dirname(os.path.abspath(__file__))
 if ROOT not in sys.path:
     sys.path.insert(0, ROOT)
 
-LAYERS = [  # name, M, K, Split_K (sizes the workspace: Split_K * M * N * 2 bytes)
-    ("qkv", 27648, 9216, 4),
-    ("out_proj", 9216, 9216, 8),
-    ("ffn1", 36864, 9216, 4),
-    ("ffn2", 9216, 36864, 8),
+# name, M, K, how the layer is split over ranks, Split_K (sizes the workspace: Split_K * M * N * 2 bytes)
+LAYERS = [
+    ("qkv", 27648, 9216, "rows", 4),
+    ("out_proj", 9216, 9216, "cols", 8),
+    ("ffn1", 36864, 9216, "rows", 4),
+    ("ffn2", 9216, 36864, "cols", 8),
+]
+# OPT-175B layer shapes of the tensor-parallel configuration (hidden 12288, FFN 49152)
+LAYERS_175B = [
+    ("qkv_175b", 36864, 12288, "rows", 4),
+    ("ffn1_175b", 49152, 12288, "rows", 4),
+    ("ffn2_175b", 12288, 49152, "cols", 8),
 ]
 N_TOKENS = 16
 SPARSITY = 0.8
 WORKLOAD = "opt66b_decoder_block_4_spmm_n16_p0.8"
+METRIC = "effective weight-HBM GB/s, SpMM (OPT-66B shapes, N=16, 80% sparse)"
 HBM_PEAK_FALLBACK_GBS = 6650.0
-# dram__bytes_read + dram__bytes_write over algorithmic bytes, from the ncu capture summarised in
-# profiles/spmm_decode_n16_ffn1_lsu_counters.md (FFN1 launch: 278.5 MB / 273.5 MB)
+ROTATE_BYTES = 256e6  # weights a timed loop cycles through: twice what L2 (126 MB) holds
+SEED_A, SEED_B = 0xA000, 0xB000
+# dram__bytes_read + dram__bytes_write over algorithmic bytes of one launch of the decode kernel, from an
+# ncu capture of the FFN1 launch (278.5 MB against 273.5 MB)
 DRAM_TRAFFIC_OVER_ALGORITHMIC = 1.018
 
 
-def measured_hbm_peak():
-    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+def measured_peak(key, fallback):
     try:
-        with open(path) as f:
-            return float(json.load(f)["hbm_gbs"]), "measured"
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)[key]), "measured"
     except Exception:
-        return HBM_PEAK_FALLBACK_GBS, "fallback"
+        return fallback, "fallback"
 
 
 class ClockSampler(threading.Thread):
@@ -74,8 +87,9 @@ class ClockSampler(threading.Thread):
             while not self._stop_flag.is_set():
                 mhz = pynvml.nvmlDeviceGetClockInfo(h, pynvml.NVML_CLOCK_SM)
                 mask = pynvml.nvmlDeviceGetCurrentClocksThrottleReasons(h)
-                self.samples.append((time.time(), mhz))
-                if self.window and self.window[0] <= time.time():
+                now = time.time()
+                self.samples.append((now, mhz))
+                if self.window and self.window[0] <= now and (self.window[1] is None or now <= self.window[1]):
                     for name, bit in names.items():
                         if mask & bit:
                             self.reasons.add(name)
@@ -88,7 +102,7 @@ class ClockSampler(threading.Thread):
         self.join(timeout=2)
 
     def summary(self, t0, t1):
-        inside = [m for (t, m) in self.samples if t0 <= t <= t1] or [m for (_, m) in self.samples[-3:]]
+        inside = [m for (t, m) in self.samples if t0 <= t <= t1]
         return {"sm_mhz": float(np.median(inside)) if inside else None, "sm_max_mhz": self.max_mhz,
                 "reasons": sorted(self.reasons), "samples": len(inside)}
 
@@ -98,11 +112,83 @@ def algorithmic_bytes(n_words, n_offsets, M, K, N):
     return 4 * n_words + 4 * n_offsets + 2 * K * N + 2 * M * N
 
 
-def make_layer(sp, name, M, K, seed):
-    A = sp.synth_fp16((M, K), seed, 0.02, SPARSITY)
-    words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, N_TOKENS, K)
-    del A
-    return words, offsets, n_offsets
+def shard_shape(M, K, split, world):
+    return (M // world, K) if split == "rows" else (M, K // world)
+
+
+def shard_block(M, K, split, rank, world):
+    """(rows, cols, row0, col0) of rank's shard inside the M x K matrix."""
+    m, k = shard_shape(M, K, split, world)
+    return (m, k, rank * m, 0) if split == "rows" else (m, k, 0, rank * k)
+
+
+# --------------------------------------------------------------------------------------------- GPU arm
+class Layer:
+    """One rank's shard of one linear layer, resident on the device, with everything the step needs."""
+
+    def __init__(self, sp, torch, dev, name, M, K, split, split_k, seed_a, seed_b, rank, world, N, keep_dense):
+        self.name, self.M_full, self.K_full, self.split, self.split_k, self.N = name, M, K, split, split_k, N
+        self.seed_a = seed_a
+        m, k, row0, col0 = shard_block(M, K, split, rank, world)
+        self.M, self.K, self.row0, self.col0 = m, k, row0, col0
+        A = sp.synth_fp16_block(m, k, K, row0, col0, seed_a, 0.02, SPARSITY)
+        words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, m, N, k)
+        self.weight_bytes = 4 * words.size + 4 * n_offsets
+        self.algo_bytes = algorithmic_bytes(words.size, n_offsets, m, k, N)
+        copies = max(1, int(np.ceil(ROTATE_BYTES / self.weight_bytes)))
+        first = torch.from_numpy(words.view(np.int32)).to(dev)
+        self.words = [first] + [first.clone() for _ in range(copies - 1)]
+        self.offsets = torch.from_numpy(offsets).to(dev)
+        B_full = sp.synth_fp16((K, N), seed_b, 1.0)
+        self.B_full = B_full
+        B_mine = B_full if split == "rows" else np.ascontiguousarray(B_full[col0:col0 + k])
+        self.B_host = torch.from_numpy(B_mine.view(np.int16)).pin_memory()
+        self.B = self.B_host.to(dev)
+        self.C = torch.zeros((m, N), dtype=torch.int16, device=dev)
+        self.C_host = torch.zeros((m, N), dtype=torch.int16).pin_memory()
+        self.ws = torch.zeros(sp.workspace_bytes(m, N, split_k) // 2, dtype=torch.int16, device=dev)
+        self.dense = None
+        if keep_dense:
+            dense_copies = max(1, int(np.ceil(ROTATE_BYTES / (2.0 * m * k))))
+            d0 = torch.from_numpy(A.view(np.float16)).to(dev)
+            self.dense = [d0] + [d0.clone() for _ in range(dense_copies - 1)]
+        self.peer = None      # two PeerAllReduce objects used alternately (row-parallel layers, world > 1)
+        self.result = self.C  # where the layer's final result lies after a step
+
+    def launch(self, sp, copy, C=None):
+        rc = sp.SpMM_SplitK_API(None, None, self.words[copy % len(self.words)], None, None, self.offsets, self.B,
+                                self.C if C is None else C, self.M, self.N, self.K, self.ws, self.split_k)
+        if rc != 0:
+            raise RuntimeError("SpMM_SplitK_API failed with cudaError %d" % rc)
+
+
+def verify_layer(sp, layer, C_bits, rows_global, label):
+    """Checks rows of the layer's result against the oracle's fp64 product (the checker, not the product):
+    max|err| <= 1e-2 max|C64| and mean relative error <= 1e-3 over the sampled rows."""
+    import oracle
+    A_rows = np.concatenate([sp.synth_fp16_block(128, layer.K_full, layer.K_full, int(r0), 0, layer.seed_a, 0.02, SPARSITY)
+                             for r0 in rows_global[::128]], axis=0)
+    c64 = oracle.spmm_f64_threads(A_rows, layer.B_full)
+    ok, max_ratio, mean_rel = oracle.tolerance_check(np.ascontiguousarray(C_bits), c64)
+    return {"layer": label, "rows": int(len(rows_global)), "ok": bool(ok), "max_err_over_max_c": float("%.3g" % max_ratio),
+            "mean_rel_err": float("%.3g" % mean_rel)}
+
+
+def sample_rows(sp, layer, rng):
+    """Local row indices to verify, whole rows of tiles: the first and the last, up to four whose K range is split
+    between thread blocks, and two more picked at random."""
+    tiles_m, tiles_k = layer.M // 128, layer.K // 64
+    cb, _, _ = sp.plan(tiles_m, tiles_k, 148, 1 << 30)
+    split = sorted({int(b) // tiles_k for b in cb[1:-1] if int(b) % tiles_k != 0})
+    picks = {0, tiles_m - 1} | set(split[:2] + split[-2:]) | set(int(x) for x in rng.integers(0, tiles_m, 2))
+    return np.concatenate([np.arange(t * 128, (t + 1) * 128) for t in sorted(picks)])
+
+
+def graph_of(torch, stream, fn):
+    g = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(g, stream=stream):
+        fn()
+    return g
 
 
 def run_ours(args):
@@ -110,6 +196,7 @@ def run_ours(args):
     import torch.distributed as dist
 
     import graphneuralnetproj_b200 as sp
+    from graphneuralnetproj_b200 import tensor_parallel as tp
 
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -119,154 +206,352 @@ def run_ours(args):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
-
-    # ---- weights: encoded on the host, resident in HBM (rank r holds row shard r of each layer)
-    layers = []
-    weight_bytes = algo_bytes = 0
-    for li, (name, M, K, sk) in enumerate(LAYERS):
-        words, offsets, n_offsets = make_layer(sp, name, M, K, 0xA000 + 16 * rank + li)
-        weight_bytes += 4 * words.size + 4 * n_offsets
-        algo_bytes += algorithmic_bytes(words.size, n_offsets, M, K, N_TOKENS)
-        B_host = torch.from_numpy(sp.synth_fp16((K, N_TOKENS), 0xB000 + li, 1.0).view(np.int16)).pin_memory()
-        layers.append(dict(
-            name=name, M=M, K=K, sk=sk,
-            words=torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev),
-            offsets=torch.from_numpy(offsets).to(dev),
-            B_host=B_host, B=B_host.to(dev),
-            C=torch.zeros((M, N_TOKENS), dtype=torch.int16, device=dev),
-            C_host=torch.zeros((M, N_TOKENS), dtype=torch.int16).pin_memory(),
-            ws=torch.zeros(sp.workspace_bytes(M, N_TOKENS, sk) // 2, dtype=torch.int16, device=dev)))
-        del words
-
-    def launch(layer):
-        rc = sp.SpMM_SplitK_API(None, None, layer["words"], None, None, layer["offsets"], layer["B"], layer["C"],
-                                layer["M"], N_TOKENS, layer["K"], layer["ws"], layer["sk"])
-        if rc != 0:
-            raise RuntimeError("SpMM_SplitK_API failed with cudaError %d" % rc)
-
-    def step():
-        for layer in layers:
-            launch(layer)
-
-    def step_e2e():
-        # the C boundary's host-buffer call: H2D copy of B, SpMM, D2H copy of C, per layer
-        for layer in layers:
-            rc = sp.SpMM_SplitK_API_host_io(stream, layer["words"], layer["offsets"], layer["B_host"], layer["C_host"],
-                                            layer["B"], layer["C"], layer["M"], N_TOKENS, layer["K"], layer["ws"], layer["sk"])
-            if rc != 0:
-                raise RuntimeError("spmm_b200_spmm_splitk_host_io failed with cudaError %d" % rc)
+    # inference weights are constant: let every launch fetch them while its predecessor drains
+    sp.set_weights_constant(os.environ.get("SPMM_WEIGHTS_CONSTANT", "1") != "0")
+    N = N_TOKENS
+    warmup = max(args.warmup, 3)
+    hbm_peak, peak_kind = measured_peak("hbm_gbs", HBM_PEAK_FALLBACK_GBS)
 
     def barrier():
         if world > 1:
             dist.barrier()
         torch.cuda.synchronize()
 
-    stream = torch.cuda.Stream()
-    with torch.cuda.stream(stream):
-        for _ in range(max(args.warmup, 3)):
-            step()
-        torch.cuda.synchronize()
-        # One step captured as a CUDA graph so that launch latency of the host loop is not timed.
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph, stream=stream):
-            step()
-        graph.replay()
-        sampler = ClockSampler(local)
-        sampler.start()
+    def reduce_max(values):
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.tolist()
+
+    def reduce_sum(values):
+        t = torch.tensor(values, dtype=torch.float64, device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.SUM)
+        return t.tolist()
+
+    def build(specs, seed_base, keep_dense):
+        out = []
+        for li, (name, M, K, split, sk) in enumerate(specs):
+            if (M if split == "rows" else K) % (world * (128 if split == "rows" else 64)):
+                raise SystemExit("%s cannot be split %d ways" % (name, world))
+            out.append(Layer(sp, torch, dev, name, M, K, split, sk, SEED_A + seed_base + li, SEED_B + seed_base + li,
+                             rank, world, N, keep_dense))
+        return out
+
+    def add_peer_reducers(some_layers):
+        for L in some_layers:
+            if L.split == "cols":
+                L.peer = [tp.PeerAllReduce(L.M * N, dev, replayable=True) for _ in range(2)]
+
+    layers = build(LAYERS, 0, True)
+    # ---- the sum over ranks of the layers split by K: NCCL all-reduce, and the library's own kernel
+    peer_ok = False
+    if world > 1:
+        try:
+            add_peer_reducers(layers)
+            peer_ok = True
+        except Exception as exc:  # symmetric memory not available on this box
+            if rank == 0:
+                print("peer-memory reduction unavailable:", exc, file=sys.stderr)
+        peer_ok = reduce_sum([1.0 if peer_ok else 0.0])[0] == world
+    modes = ["none"] if world == 1 else (["peer", "nccl", "none"] if peer_ok else ["nccl", "none"])
+    main_mode = modes[0]
+
+    def run_layer(L, copy, mode, use):
+        """SpMM of layer L (+ the sum over ranks for a layer split by K).  `use`: running count of uses of L, for the
+        alternation between its two peer-reduction objects."""
+        if L.split == "cols" and mode == "peer":
+            red = L.peer[use & 1]
+            L.launch(sp, copy, red.next_buffer().view(torch.int16).view(L.M, N))
+            L.result = red.reduce().view(torch.int16).view(L.M, N)
+        else:
+            L.launch(sp, copy)
+            if L.split == "cols" and mode == "nccl":
+                dist.all_reduce(L.C.view(torch.float16), op=dist.ReduceOp.SUM)
+            L.result = L.C
+
+    def time_launches(stream, fn, count):
+        """us per call of fn: a CUDA graph of `count` calls (count even), replayed five times."""
+        g = graph_of(torch, stream, lambda: [fn(i) for i in range(count)])
+        g.replay()
         barrier()
         e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        t0 = time.time()
-        sampler.window = (t0, None)
         e0.record(stream)
-        for _ in range(args.steps):
-            graph.replay()
+        for _ in range(5):
+            g.replay()
         e1.record(stream)
         barrier()
-        t1 = time.time()
-        sampler.stop()
-        ms = e0.elapsed_time(e1)
+        return reduce_max([e0.elapsed_time(e1) * 1000.0 / (5 * count)])[0]
 
-        # per-layer device time: events around every launch of a few plain (un-captured) steps, so
-        # each layer's weights have been evicted from L2 by the other layers in between
-        reps, pairs = 10, []
-        for _ in range(reps):
-            for layer in layers:
-                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                a.record(stream)
-                launch(layer)
-                b.record(stream)
-                pairs.append((layer["name"], a, b))
+    def layer_record(stream, L, with_cublas):
+        count = max(8, 2 * len(L.words))
+        entry = {"shard": [L.M, L.K], "split": L.split if world > 1 else "none",
+                 "spmm_us": round(time_launches(stream, lambda i: L.launch(sp, i), count), 2)}
+        if L.split == "cols" and world > 1:
+            for mode in modes[:-1]:
+                entry["spmm_plus_%s_reduce_us" % mode] = round(
+                    time_launches(stream, lambda i, mode=mode: run_layer(L, i, mode, i), count), 2)
+        if with_cublas and L.dense is not None:
+            Bh = L.B.view(torch.float16)
+            out = torch.empty((L.M, N), dtype=torch.float16, device=dev)
+            count_d = max(8, 2 * len(L.dense))
+            entry["cublas_dense_us"] = round(
+                time_launches(stream, lambda i: torch.matmul(L.dense[i % len(L.dense)], Bh, out=out), count_d), 2)
+            entry["speedup_vs_cublas"] = round(entry["cublas_dense_us"] / entry["spmm_us"], 3)
+        entry["roofline_frac"] = round(L.algo_bytes / entry["spmm_us"] / 1e3 / hbm_peak, 4)
+        return entry
+
+    def verify(some_layers, mode, seed):
+        """Runs two steps and checks sampled rows of every layer's result on every rank against the fp64 oracle."""
+        for i in range(2):
+            for L in some_layers:
+                run_layer(L, i, mode, i)
         torch.cuda.synchronize()
-        per_layer = {}
-        for name, a, b in pairs:
-            per_layer[name] = per_layer.get(name, 0.0) + a.elapsed_time(b) * 1000.0 / reps
+        rng = np.random.default_rng(seed + rank)
+        checks = []
+        for L in some_layers:
+            rows_local = sample_rows(sp, L, rng)
+            C_bits = L.result.cpu().numpy().view(np.uint16)[rows_local]
+            checks.append(verify_layer(sp, L, C_bits, rows_local + L.row0, L.name))
+        all_ok = all(c["ok"] for c in checks) and sp.device_status() == 0
+        return reduce_sum([1.0 if all_ok else 0.0])[0] == world, checks
 
-        # end to end: activations from pinned host memory, results back to the host, every launch
-        for _ in range(3):
-            step_e2e()
+    max_copies = max(len(L.words) for L in layers)
+    stream = torch.cuda.Stream()
+    record = {}
+    with torch.cuda.stream(stream):
+        # ---- warm-up, un-captured, through every mode
+        for mode in modes:
+            for i in range(warmup):
+                for L in layers:
+                    run_layer(L, i, mode, i)
         barrier()
-        f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        f0.record(stream)
-        for _ in range(args.steps):
-            step_e2e()
-        f1.record(stream)
+        # ---- what the timed loop computes is checked before it is timed
+        verified, checks = verify(layers, main_mode, 1234)
+
+        # ---- one CUDA graph per weight copy and mode: a step = the four layers (+ sums over ranks)
+        graphs = {mode: [graph_of(torch, stream, lambda c=c, mode=mode: [run_layer(L, c, mode, c) for L in layers])
+                         for c in range(max_copies)] for mode in modes}
+        for mode in modes:
+            for g in graphs[mode]:
+                g.replay()
         barrier()
-        ms_e2e = f0.elapsed_time(f1)
+
+        def time_block(mode, steps):
+            """Device time of exactly `steps` steps, bracketed by a barrier and a synchronise on both sides."""
+            gs = graphs[mode]
+            barrier()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record(stream)
+            for i in range(steps):
+                gs[i % len(gs)].replay()
+            e1.record(stream)
+            barrier()
+            return e0.elapsed_time(e1)
+
+        # ---- the timed region: repeats of a block of K steps until at least half a second has been timed
+        probe = reduce_max([time_block(main_mode, args.steps)])[0]
+        repeats = int(min(400, max(5, np.ceil(500.0 / max(probe, 1e-3)))))
+        sampler = ClockSampler(local)
+        sampler.start()
+        time.sleep(0.02)
+        t0 = time.time()
+        sampler.window = (t0, None)
+        blocks = [time_block(main_mode, args.steps) for _ in range(repeats)]
+        t1 = time.time()
+        sampler.window = (t0, t1)
+        sampler.stop()
+        blocks = reduce_max(blocks)  # per repeat, the slowest rank
+        ms_per_step = float(np.median(blocks)) / args.steps
+        record["ms_per_step_min_max"] = [round(min(blocks) / args.steps, 5), round(max(blocks) / args.steps, 5)]
+        record["repeats"] = repeats
+        other_modes = {}
+        for mode in modes[1:]:
+            ms = [time_block(mode, args.steps) for _ in range(5)]
+            other_modes[mode] = float(np.median(reduce_max(ms))) / args.steps
+
+        # ---- per layer: a graph of back-to-back launches of that layer alone, rotating through its copies
+        per_layer = {L.name: layer_record(stream, L, True) for L in layers}
+
+        # ---- end to end: activations from pinned host memory, results back to the host, every step
+        if world == 1:
+            items = [sp.host_io_items([dict(Compressed_A=L.words[c % len(L.words)], TileOffsets=L.offsets, B_host=L.B_host,
+                                             C_host=L.C_host, B_dev=L.B, C_dev=L.C, M=L.M, N=N, K=L.K,
+                                             Reduction_Workspace=L.ws, Split_K=L.split_k) for L in layers])
+                     for c in range(max_copies)]
+
+            def step_e2e(i):
+                rc = sp.SpMM_SplitK_API_host_io_batch(stream, items[i % max_copies])
+                if rc != 0:
+                    raise RuntimeError("spmm_b200_spmm_splitk_host_io_batch failed with cudaError %d" % rc)
+        else:
+            def step_e2e(i):
+                for L in layers:
+                    L.B.copy_(L.B_host, non_blocking=True)
+                    run_layer(L, i, main_mode, i)
+                    L.C_host.copy_(L.result, non_blocking=True)
+
+        for i in range(3):
+            step_e2e(i)
+        e2e_blocks = []
+        for _ in range(5):
+            barrier()
+            f0, f1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            f0.record(stream)
+            for i in range(args.steps):
+                step_e2e(i)
+            f1.record(stream)
+            barrier()
+            e2e_blocks.append(f0.elapsed_time(f1))
+        ms_e2e = float(np.median(reduce_max(e2e_blocks))) / args.steps
+        e2e_ok = all(bool(np.array_equal(L.C_host.numpy(), L.result.cpu().numpy())) for L in layers)
+
+        extras = {}
+        if not args.no_extras:
+            # OPT-175B layer shapes sharded over the ranks: QKV and FFN1 by rows, FFN2 by K with the sum over ranks
+            big = build(LAYERS_175B, 0x50, False)
+            if "peer" in modes:
+                add_peer_reducers(big)
+            for mode in modes:
+                for L in big:
+                    run_layer(L, 0, mode, 0)
+                    run_layer(L, 1, mode, 1)
+            big_ok, big_checks = verify(big, main_mode, 99)
+            extras["config5"] = {L.name: layer_record(stream, L, False) for L in big}
+            extras["config5"]["verified"] = bool(big_ok)
+            extras["config5"]["verification"] = big_checks
+            verified = verified and big_ok
+            del big
+            torch.cuda.empty_cache()
+            if world == 1:
+                extras["prefill"] = prefill_point(sp, torch, dev, 12288, 12288, 1024, 0.8)
+
     status = sp.device_status()
     if status != 0:
         raise RuntimeError("device status %d: a bounded wait inside the kernel gave up" % status)
-
-    times = torch.tensor([ms, ms_e2e], dtype=torch.float64, device=dev)
-    if world > 1:
-        dist.all_reduce(times, op=dist.ReduceOp.MAX)
-    ms, ms_e2e = times.tolist()
+    if world > 1 and peer_ok and sp.spmm_api.LIB.spmm_b200_allreduce_status(0) != 0:
+        raise RuntimeError("a wait inside the peer-memory reduction ran out")
+    weight_bytes, algo_bytes = reduce_sum([sum(L.weight_bytes for L in layers), sum(L.algo_bytes for L in layers)])
     if rank != 0:
         if world > 1:
             dist.destroy_process_group()
         return
-    ms_per_step = ms / args.steps
-    value = world * weight_bytes / (ms_per_step * 1e-3) / 1e9
-    e2e_value = world * weight_bytes / (ms_e2e / args.steps * 1e-3) / 1e9
-    peak, peak_kind = measured_hbm_peak()
-    achieved = algo_bytes / (ms_per_step * 1e-3) / 1e9  # this rank's kernel launches
+    value = weight_bytes / (ms_per_step * 1e-3) / 1e9
+    achieved = algo_bytes / world / (ms_per_step * 1e-3) / 1e9  # per GPU: the roofline is a per-GPU figure
+    launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode == "peer" else 0)
+    reduce_note = {"none": "no collective (one GPU)", "peer": "library kernel over peer memory (NVLink loads, no multicast)",
+                   "nccl": "NCCL all-reduce"}[main_mode]
     line = {
-        "metric": "effective weight-HBM GB/s, SpMM (OPT-66B shapes, N=16, 80% sparse)",
-        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
-        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "metric": METRIC,
+        "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": round(ms_per_step, 5), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "layers": [[n, m, k] for n, m, k, _ in LAYERS], "n_tokens": N_TOKENS,
-                   "sparsity": SPARSITY, "split_k": [s for *_, s in LAYERS], "parallelism": "column-parallel by M x%d" % world,
-                   "l2_policy": "inputs larger than L2: %.0f MB of weights per step" % (weight_bytes / 1e6),
-                   "spmm_us_per_layer": {k: round(v, 2) for k, v in per_layer.items()},
-                   "weight_bytes_per_step_per_gpu": weight_bytes},
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": peak, "unit": "GB/s",
-                     "frac": round(achieved / peak, 4),
-                     "traffic": int(algo_bytes * DRAM_TRAFFIC_OVER_ALGORITHMIC),
-                     "traffic_note": "bytes per step (4 launches): ncu dram read+write of one launch / its algorithmic "
-                                     "bytes = 1.018 (FFN1: 278.5 MB against 273.5 MB), applied to the step", "peak_source": peak_kind,
-                     "kernel": "spmm_decode_kernel<16>", "algorithmic_bytes_per_step": algo_bytes},
-        "e2e": {"value": round(e2e_value, 1), "unit": "GB/s",
-                "h2d_bytes_per_step": sum(2 * L["K"] * N_TOKENS for L in layers),
-                "d2h_bytes_per_step": sum(2 * L["M"] * N_TOKENS for L in layers)},
-        "gpu_launches": args.steps * len(layers),
+        "config": {"workload": WORKLOAD, "layers": [[n, m, k] for n, m, k, _, _ in LAYERS], "n_tokens": N,
+                   "sparsity": SPARSITY, "split_k": [s for *_, s in LAYERS],
+                   "parallelism": "one GPU" if world == 1 else
+                   "tensor-parallel x%d: qkv, ffn1 by rows (no collective); out_proj, ffn2 by K + sum over ranks (%s)"
+                   % (world, reduce_note),
+                   "l2_policy": "weights rotate through copies: %.0f MB per GPU between two uses of the same bytes"
+                                % (sum(L.weight_bytes * len(L.words) for L in layers) / 1e6),
+                   "weights_constant": os.environ.get("SPMM_WEIGHTS_CONSTANT", "1") != "0",
+                   "per_layer": per_layer, "weight_bytes_per_step": int(weight_bytes)},
+        "verified": bool(verified), "verification": checks,
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": hbm_peak, "unit": "GB/s",
+                     "frac": round(achieved / hbm_peak, 4),
+                     "traffic": int(algo_bytes / world * DRAM_TRAFFIC_OVER_ALGORITHMIC),
+                     "traffic_note": "bytes per step per GPU (4 launches): ncu dram read+write of one launch / its "
+                                     "algorithmic bytes = 1.018 (FFN1: 278.5 MB against 273.5 MB), applied to the step",
+                     "peak_source": peak_kind, "kernel": "spmm_decode_kernel<16>",
+                     "algorithmic_bytes_per_step_per_gpu": int(algo_bytes / world)},
+        "e2e": {"value": round(weight_bytes / (ms_e2e * 1e-3) / 1e9, 1), "unit": "GB/s",
+                "h2d_bytes_per_step": int(sum(2 * L.K * N for L in layers)),
+                "d2h_bytes_per_step": int(sum(2 * L.M * N for L in layers)),
+                "results_match_device_call": bool(e2e_ok),
+                "call": "spmm_b200_spmm_splitk_host_io_batch (copies overlap the products)" if world == 1 else
+                        "per layer: copy B from pinned memory, SpMM (+ sum over ranks), copy C to pinned memory"},
+        "gpu_launches": args.steps * launches_per_step,
         "clocks": sampler.summary(t0, t1),
     }
+    line.update(record)
+    if world > 1:
+        line["step_us_by_reduction"] = {main_mode: round(ms_per_step * 1e3, 2),
+                                        **{m: round(v * 1e3, 2) for m, v in other_modes.items()}}
+        line["comm_nranks_seen"] = world
+    step_cublas = sum(e.get("cublas_dense_us", 0.0) for e in per_layer.values())
+    if step_cublas:
+        step_spmm = sum(e["spmm_us"] for e in per_layer.values())
+        line["vs_cublas"] = {"cublas_dense_us_per_step": round(step_cublas, 2), "spmm_us_per_step": round(step_spmm, 2),
+                             "speedup": round(step_cublas / step_spmm, 3),
+                             "note": "cuBLAS dense fp16 (fp32 accumulate) on this GPU's pruned shard, same rotation through L2"}
+    line.update(extras)
     if world == 1 and not args.no_cpu_baseline:
         line["cpu_baseline"] = cpu_baseline()
+    if not verified:
+        line["error"] = "verification against the fp64 oracle failed"
     print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
+    if not verified:
+        raise SystemExit(1)
 
 
-def cpu_sample_problem(sp, rows, K, seed):
-    A = sp.synth_fp16((rows, K), seed, 0.02, SPARSITY)
-    B = sp.synth_fp16((K, N_TOKENS), seed + 1, 1.0)
-    return A, B
+def prefill_point(sp, torch, dev, M, K, N, p):
+    """One prefill-size point: dense-equivalent TFLOP/s = 2*M*N*K / t against the measured dense tensor peak."""
+    tensor_peak = measured_peak("bf16_tflops", 1590.0)[0]
+    A = sp.synth_fp16((M, K), 0xA300 + int(p * 100), 0.02, p)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, 64, K)
+    wd = torch.from_numpy(words.view(np.int32)).to(dev)
+    od = torch.from_numpy(offsets).to(dev)
+    Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB300, 1.0).view(np.int16)).to(dev)
+    Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
+    ws = torch.zeros(sp.workspace_bytes(M, N, 2) // 2, dtype=torch.int16, device=dev)
+    for _ in range(3):
+        assert sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 2) == 0
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    reps = 5
+    e0.record()
+    for _ in range(reps):
+        sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 2)
+    e1.record()
+    torch.cuda.synchronize()
+    us = e0.elapsed_time(e1) * 1000.0 / reps
+    return {"M": M, "K": K, "N": N, "sparsity": p, "spmm_us": round(us, 1),
+            "dense_equiv_tflops": round(2.0 * M * N * K / us / 1e6, 1),
+            "frac_of_tensor_peak": round(2.0 * M * N * K / us / 1e6 / tensor_peak, 4), "tensor_peak_tflops": tensor_peak}
 
 
-def cpu_spmm_threads(oracle, words, offsets, B, M, K, threads):
+# --------------------------------------------------------------------------------------------- CPU arms
+# Nothing below imports the product package: inputs come from the oracle's own generator, the encoder is the
+# reference's (oracle/_ref) or its C restatement, the product is the oracle's decode + fp32-accumulate loop.
+def cpu_layers(fraction, threads):
+    """The four layers of the step, the first `fraction` of each layer's rows of tiles:
+    ([(words, offsets, B, rows, K)], seconds the slowest encoder call took)."""
+    import oracle
+    results = [None] * len(LAYERS)
+
+    def make(li):
+        name, M, K, _, _ = LAYERS[li]
+        rows = max(128, int(M * fraction) // 128 * 128)
+        A = oracle.synth_fp16_block(rows, K, K, 0, 0, SEED_A + li, 0.02, SPARSITY, threads=max(1, threads // len(LAYERS)))
+        B = oracle.synth_fp16_block(K, N_TOKENS, N_TOKENS, 0, 0, SEED_B + li, 1.0, threads=1)
+        t0 = time.time()
+        words, offsets = (oracle.ref_encode(A) if oracle.have_ref() else oracle.encode(A))
+        results[li] = ((words, offsets, B, rows, K), time.time() - t0)
+
+    pool = [threading.Thread(target=make, args=(li,)) for li in range(len(LAYERS))]
+    for th in pool:
+        th.start()
+    for th in pool:
+        th.join()
+    return [r for r, _ in results], max(s for _, s in results)
+
+
+def cpu_spmm_threads(words, offsets, B, M, K, threads):
     """The oracle's decode + fp32-accumulate product over row blocks of tiles, one block per host thread."""
+    import oracle
     tiles_m, tiles_k = M // 128, K // 64
     threads = max(1, min(threads, tiles_m))
     out = [None] * threads
@@ -286,77 +571,77 @@ def cpu_spmm_threads(oracle, words, offsets, B, M, K, threads):
     return np.concatenate(out, axis=0)
 
 
+def cpu_step(layers, threads):
+    for words, offsets, B, rows, K in layers:
+        cpu_spmm_threads(words, offsets, B, rows, K, threads)
+
+
 def cpu_baseline():
-    """Reference CPU path on a bounded sample: the reference's own InitSparseMatrixA_API (one
-    core; it is single-threaded) and the oracle's decode + fp32 host product (one core)."""
-    import graphneuralnetproj_b200 as sp
+    """The CPU path on a bounded sample, timed beside the GPU number: the reference's own InitSparseMatrixA_API
+    (single-threaded as shipped, one thread per layer here) and the oracle's decode + fp32 host product on all host
+    threads, over the first eighth of the rows of every layer of the step."""
     import oracle
-    M, K = 9216, 9216  # the out-proj layer of the step
-    A, B = cpu_sample_problem(sp, M, K, 0xC000)
+    cores = os.cpu_count() or 1
+    layers, enc_s = cpu_layers(0.125, cores)
+    cpu_step(layers, cores)
     t0 = time.time()
-    if oracle.have_ref():
-        words, offsets = oracle.ref_encode(A)
-        encoder = "reference InitSparseMatrixA_API (oracle/_ref)"
-    else:
-        words, offsets = oracle.encode(A)
-        encoder = "oracle port of InitSparseMatrixA_API"
-    t_enc = time.time() - t0
-    t0 = time.time()
-    oracle.spmm_from_csl(words, offsets, B, M, K)
-    t_spmm = time.time() - t0
-    wbytes = 4 * words.size + 4 * offsets.size
-    return {"value": round(wbytes / t_spmm / 1e9, 4), "unit": "GB/s", "cores": 1, "kind": "port",
-            "sample": "out-proj layer 9216x9216, N=16, p=0.8: %s %.2f s on 1 core; oracle decode + fp32 host "
-                      "product %.2f s on 1 core (value = weight bytes / product time)" % (encoder, t_enc, t_spmm),
-            "encode_s": round(t_enc, 3), "spmm_s": round(t_spmm, 3)}
+    reps = 3
+    for _ in range(reps):
+        cpu_step(layers, cores)
+    dt = (time.time() - t0) / reps
+    wbytes = sum(4 * w.size + 4 * o.size for w, o, *_ in layers)
+    return {"value": round(wbytes / dt / 1e9, 4), "unit": "GB/s", "cores": cores,
+            "kind": "reference" if oracle.have_ref() else "port",
+            "sample": "first 1/8 of the rows of each of the four layers (N=16, p=0.8): encoder %s, slowest layer %.2f s "
+                      "on 1 core; decode + fp32 host product (oracle C code) %.3f s per pass on %d threads"
+                      % ("InitSparseMatrixA_API of the compiled reference (oracle/_ref)" if oracle.have_ref()
+                         else "oracle restatement of InitSparseMatrixA_API", enc_s, dt, cores),
+            "encode_s": round(enc_s, 3), "spmm_s": round(dt, 4)}
 
 
 def run_reference(args):
-    """The reference's CPU implementation of the path on all host cores: decode of the tiled-CSL
-    words + fp32-accumulate host product, a bounded row sample of the out-proj layer per step."""
+    """The reference's CPU implementation of the path on all host cores: its InitSparseMatrixA_API encoding (outside
+    the timed loop, as the GPU arm's) and per step the decode of the tiled-CSL words + fp32-accumulate host product of
+    all four layers of the block (a bounded share of every layer's rows if a full step would take too long)."""
     if int(os.environ.get("RANK", "0")) != 0:
         return
-    import graphneuralnetproj_b200 as sp
     import oracle
     cores = os.cpu_count() or 1
-    K = 9216
-    rows = 9216
-    A, B = cpu_sample_problem(sp, rows, K, 0xC000)
-    words, offsets = (oracle.ref_encode(A) if oracle.have_ref() else oracle.encode(A))
+    # probe on 1/16 of the rows, then size the sample so that the whole run stays within about two minutes
+    probe_layers, _ = cpu_layers(1.0 / 16, cores)
+    cpu_step(probe_layers, cores)
     t0 = time.time()
-    cpu_spmm_threads(oracle, words, offsets, B, rows, K, cores)
-    probe = time.time() - t0
-    # bound the whole run to about two minutes
-    budget = 120.0 / max(args.steps + args.warmup, 1)
-    if probe > budget:
-        rows = max(128, int(rows * budget / probe) // 128 * 128)
-        tiles_k = K // 64
-        offs = offsets[:rows // 128 * tiles_k + 1]
-        offsets = np.concatenate([offs, offs[-1:]]).astype(np.int32)
-        words = words[:int(offs[-1]) * 4]
+    cpu_step(probe_layers, cores)
+    probe = (time.time() - t0) * 16
+    budget = 100.0 / max(args.steps + args.warmup, 1)
+    fraction = 1.0 if probe <= budget else max(1.0 / 16, budget / probe)
+    layers = probe_layers if fraction <= 1.0 / 16 else cpu_layers(fraction, cores)[0]
     for _ in range(args.warmup):
-        cpu_spmm_threads(oracle, words, offsets, B, rows, K, cores)
+        cpu_step(layers, cores)
     t0 = time.time()
     for _ in range(args.steps):
-        cpu_spmm_threads(oracle, words, offsets, B, rows, K, cores)
+        cpu_step(layers, cores)
     dt = (time.time() - t0) / args.steps
-    wbytes = 4 * words.size + 4 * offsets.size
+    wbytes = sum(4 * w.size + 4 * o.size for w, o, *_ in layers)
     value = round(wbytes / dt / 1e9, 4)
-    sample = "%d x %d rows of the out-proj layer per step, N=16, p=0.8, %d host threads" % (rows, K, cores)
+    sample = ("all four layers of the block, %s of every layer's rows per step, N=16, p=0.8, %d host threads; encoder: %s"
+              % ("all" if fraction >= 1.0 else "the first %.3f" % fraction, cores,
+                 "reference (oracle/_ref)" if oracle.have_ref() else "oracle restatement"))
     line = {
-        "impl": "reference", "metric": "effective weight-HBM GB/s, SpMM (OPT-66B shapes, N=16, 80% sparse)",
+        "impl": "reference", "metric": METRIC,
         "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
-        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "sample": sample},
+        "config": {"workload": WORKLOAD, "layers": [[n, m, k] for n, m, k, _, _ in LAYERS], "n_tokens": N_TOKENS,
+                   "sparsity": SPARSITY, "rows_fraction_per_step": round(fraction, 4)},
         "cpu_baseline": {"value": value, "unit": "GB/s", "cores": cores,
-                         "kind": "port", "sample": sample + "; encoder: " +
-                         ("reference (oracle/_ref)" if oracle.have_ref() else "oracle port")},
+                         "kind": "reference" if oracle.have_ref() else "port", "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line), flush=True)
 
 
+# --------------------------------------------------------------------------------------------- sweeps
 def run_sweep(args):
     """Decode-size sweep over the OPT-66B layer shapes, N and sparsity (one JSON line per point),
     with cuBLAS dense fp16 on the pruned matrix as the comparator.  Device-timed with CUDA graphs;
@@ -366,9 +651,10 @@ def run_sweep(args):
     import graphneuralnetproj_b200 as sp
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
-    peak, _ = measured_hbm_peak()
+    peak, _ = measured_peak("hbm_gbs", HBM_PEAK_FALLBACK_GBS)
+    sp.set_weights_constant(True)
     # "cfg1" = the reference's single-SpMM case (M = K = 7168 with its Split_K hint 5), beside the OPT-66B layers
-    shapes = [(n, m, k, 8) for n, m, k, _ in LAYERS if n in args.sweep_layers.split(",")]
+    shapes = [(n, m, k, 8) for n, m, k, _, _ in LAYERS if n in args.sweep_layers.split(",")]
     if "cfg1" in args.sweep_layers.split(","):
         shapes.append(("cfg1", 7168, 7168, 5))
     n_list = [int(x) for x in args.sweep_n.split(",")]
@@ -379,7 +665,7 @@ def run_sweep(args):
             words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, 16, K)
             wbytes = 4 * words.size + 4 * n_offsets
             copies = max(1, int(np.ceil(256e6 / wbytes)))
-            wds = [torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+            wds = [torch.from_numpy(words.view(np.int32)).to(dev)
                    for _ in range(copies)]
             od = torch.from_numpy(offsets).to(dev)
             dense = [torch.from_numpy(A.view(np.float16)).to(dev) for _ in range(max(1, min(copies, 2)))]
@@ -436,17 +722,13 @@ def run_prefill(args):
     import graphneuralnetproj_b200 as sp
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
-    try:
-        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
-            tensor_peak = float(json.load(f)["bf16_tflops"])
-    except Exception:
-        tensor_peak = 1590.0
+    tensor_peak = measured_peak("bf16_tflops", 1590.0)[0]
     shapes = [(12288, 12288), (49152, 12288)] if not args.small else [(12288, 12288)]
     for M, K in shapes:
         for p in [float(x) for x in args.prefill_p.split(",")]:
             A = sp.synth_fp16((M, K), 0xA300 + int(p * 100), 0.02, p)
             words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, 64, K)
-            wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+            wd = torch.from_numpy(words.view(np.int32)).to(dev)
             od = torch.from_numpy(offsets).to(dev)
             Ad = torch.from_numpy(A.view(np.float16)).to(dev)
             del A, words
@@ -479,96 +761,6 @@ def run_prefill(args):
     assert sp.device_status() == 0
 
 
-def run_row_parallel(args):
-    """Row-parallel (by K) layer across the GPUs of the box: every rank multiplies its K shard of an
-    FFN2-shaped layer (M = 9216, 36864 columns of A per rank) and one NCCL sum all-reduce of the M x N
-    result finishes it.  Prints one JSON line with the SpMM-only and the SpMM + reduce time (device-timed,
-    max over ranks)."""
-    import torch
-    import torch.distributed as dist
-
-    import graphneuralnetproj_b200 as sp
-    from graphneuralnetproj_b200.tensor_parallel import RowParallelSpMM
-
-    rank = int(os.environ.get("RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    local = int(os.environ.get("LOCAL_RANK", "0"))
-    torch.cuda.set_device(local)
-    dev = torch.device("cuda", local)
-    if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
-    M, K_shard, N = 9216, 36864, N_TOKENS
-    words, offsets, n_offsets = make_layer(sp, "ffn2", M, K_shard, 0xA500 + rank)
-    wbytes = 4 * words.size + 4 * n_offsets
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
-    od = torch.from_numpy(offsets).to(dev)
-    Bd = torch.from_numpy(sp.synth_fp16((K_shard, N), 0xB500 + rank, 1.0).view(np.int16)).to(dev)
-    layer = RowParallelSpMM(wd, od, M, N, K_shard, split_k=8)
-    # a second layer's worth of weights between timed launches keeps the first one out of L2
-    other = RowParallelSpMM(wd.clone(), od, M, N, K_shard, split_k=8)
-
-    def timed(fn):
-        for _ in range(max(args.warmup, 3)):
-            fn()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        e0.record()
-        for _ in range(args.steps):
-            fn()
-        e1.record()
-        torch.cuda.synchronize()
-        t = torch.tensor([e0.elapsed_time(e1) / args.steps], dtype=torch.float64, device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return float(t.item())
-
-    def spmm_only():
-        for l in (layer, other):
-            rc = sp.SpMM_SplitK_API(None, None, l.words, None, None, l.offsets, Bd, l.C, M, N, K_shard, l.workspace, 8)
-            assert rc == 0
-
-    def with_reduce():
-        for l in (layer, other):
-            l.forward(Bd)
-
-    ms_spmm = timed(spmm_only) / 2
-    ms_full = timed(with_reduce) / 2
-    # the same with the library's own reduction kernel over peer memory instead of NCCL
-    ms_peer = None
-    if world > 1:
-        try:
-            peer_layers = [RowParallelSpMM(l.words, l.offsets, M, N, K_shard, split_k=8, reduce="peer") for l in (layer, other)]
-
-            def with_peer_reduce():
-                for l in peer_layers:
-                    l.forward(Bd)
-
-            ms_peer = timed(with_peer_reduce) / 2
-            assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
-        except Exception as exc:  # symmetric memory not available on this box
-            if rank == 0:
-                print("peer-memory reduction unavailable:", exc, file=sys.stderr)
-    assert sp.device_status() == 0
-    if rank == 0:
-        peak, src = measured_hbm_peak()
-        print(json.dumps({
-            "metric": "effective weight-HBM GB/s, row-parallel SpMM + all-reduce (FFN2 shape, N=16, 80% sparse)",
-            "value": round(world * wbytes / ((ms_peer or ms_full) * 1e-3) / 1e9, 1), "unit": "GB/s", "n_gpus": world,
-            "steps": args.steps, "warmup": max(args.warmup, 3), "scaling": "weak", "higher_is_better": True,
-            "spmm_only_us": round(ms_spmm * 1e3, 2), "spmm_plus_allreduce_us": round(ms_full * 1e3, 2),
-            "spmm_plus_peer_reduce_us": round(ms_peer * 1e3, 2) if ms_peer else None,
-            "spmm_only_gbs_per_gpu": round(wbytes / (ms_spmm * 1e-3) / 1e9, 1),
-            "allreduce_bytes": M * N * 2,
-            "config": {"workload": "row_parallel_ffn2", "M": M, "K_per_rank": K_shard, "n_tokens": N, "sparsity": SPARSITY,
-                       "parallelism": "row-parallel by K x%d; value uses the library's peer-memory reduction when "
-                                      "available, the NCCL all-reduce otherwise; both are listed" % world},
-            "roofline_frac_spmm_only": round(wbytes / (ms_spmm * 1e-3) / 1e9 / peak, 4), "peak_source": src}))
-    if world > 1:
-        dist.destroy_process_group()
-
-
 def prune_2_of_4(A_bits, keep_prob, seed):
     """2:4 magnitude pruning along K, then each survivor is zeroed with probability 1 - keep_prob."""
     groups = np.abs(A_bits.view(np.float16).astype(np.float32)).reshape(-1, 4)
@@ -591,7 +783,8 @@ def run_hetero(args):
     import graphneuralnetproj_b200 as sp
     dev = torch.device("cuda:0")
     torch.cuda.set_device(0)
-    peak, _ = measured_hbm_peak()
+    peak, _ = measured_peak("hbm_gbs", HBM_PEAK_FALLBACK_GBS)
+    sp.set_weights_constant(True)
     M = K = args.hetero_size
     N = args.hetero_n
 
@@ -634,11 +827,11 @@ def run_hetero(args):
         residual_bytes = 0
         if residual_nnz:
             rw, ro, rn = sp.InitSparseMatrixA_API(A2, M, N, K)
-            r_wds = [torch.from_numpy(np.concatenate([rw, np.zeros(4, np.uint32)]).view(np.int32)).to(dev) for _ in range(copies)]
+            r_wds = [torch.from_numpy(rw.view(np.int32)).to(dev) for _ in range(copies)]
             r_od = torch.from_numpy(ro).to(dev)
             residual_bytes = 4 * rw.size + 4 * rn
         words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, M, N, K)
-        wds = [torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev) for _ in range(copies)]
+        wds = [torch.from_numpy(words.view(np.int32)).to(dev) for _ in range(copies)]
         od = torch.from_numpy(offsets).to(dev)
         csl_bytes = 4 * words.size + 4 * n_offsets
         Ad = [torch.from_numpy(A.view(np.float16)).to(dev) for _ in range(copies)]
@@ -673,10 +866,11 @@ def run_hetero(args):
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=1000)
+    ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-extras", action="store_true", help="skip the OPT-175B and prefill sub-records of the bench line")
     ap.add_argument("--sweep", action="store_true", help="decode-size sweep (layers x N x sparsity) instead of the bench line")
     ap.add_argument("--sweep-n", default="8,16,32,64")
     ap.add_argument("--sweep-p", default="0.7,0.8,0.9")
@@ -685,14 +879,11 @@ def main():
     ap.add_argument("--prefill-n", default="256,512,1024,2048")
     ap.add_argument("--prefill-p", default="0.5,0.7,0.8")
     ap.add_argument("--small", action="store_true", help="with --prefill: only the 12288 x 12288 shape")
-    ap.add_argument("--row-parallel", action="store_true", help="row-parallel (by K) layer with an NCCL all-reduce, one rank per GPU")
     ap.add_argument("--hetero", action="store_true", help="heterogeneous decomposition points (structured half on the sparse tensor core)")
     ap.add_argument("--hetero-size", type=int, default=12288)
     ap.add_argument("--hetero-n", type=int, default=32)
     args = ap.parse_args()
-    if args.row_parallel:
-        run_row_parallel(args)
-    elif args.hetero:
+    if args.hetero:
         run_hetero(args)
     elif args.prefill:
         run_prefill(args)

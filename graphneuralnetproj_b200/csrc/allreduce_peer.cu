@@ -13,6 +13,8 @@
 // Flags carry the call's epoch, which only grows, so nothing is reset; the callers alternate between
 // two result buffers, so a fast rank's next SpMM never overwrites what a slow peer is still reading
 // (a rank reaches the flag exchange of call n + 1 only after its reads of call n have finished).
+// The epoch comes from the host, or -- so that the call can be captured in a CUDA graph and replayed --
+// from a counter in device memory that the last block of every launch advances.
 //
 // The buffers and flag arrays are symmetric allocations mapped into every rank's address space by
 // the caller (torch.distributed._symmetric_memory in the Python mirror); this file only takes
@@ -37,7 +39,8 @@ struct AllReduceParams {
     uint4*       out;                 // local result
     size_t       vectors;             // count / 8
     int          rank, world;
-    uint32_t     epoch;
+    uint32_t     epoch;               // this call's epoch when `state` is null
+    uint32_t*    state;               // or: state[0] = epoch of the previous call, state[1] = blocks finished
     unsigned long long limit_ns;
 };
 
@@ -47,10 +50,17 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
     ptx::grid_dependency_wait();  // the SpMM before this kernel in the stream wrote this rank's partial result
     if (threadIdx.x == 0)
         ok = 1;
+    uint32_t epoch = p.epoch;
+    if (p.state != nullptr) {
+        // every earlier launch that used this state has completed (stream order), so the counter is stable
+        uint32_t previous;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.state) : "memory");
+        epoch = previous + 1;
+    }
     if (blockIdx.x == 0 && threadIdx.x < p.world) {
         // this rank's partial result is complete and visible: tell peer threadIdx.x
         __threadfence_system();
-        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.rank), "r"(p.epoch) : "memory");
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.rank), "r"(epoch) : "memory");
     }
     __syncthreads();
     if (threadIdx.x < p.world) {
@@ -59,7 +69,7 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
         for (unsigned polls = 0;; polls++) {
             uint32_t seen;
             asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
-            if (static_cast<int32_t>(seen - p.epoch) >= 0)
+            if (static_cast<int32_t>(seen - epoch) >= 0)
                 break;
             if ((polls & 255u) == 255u && ptx::global_timer_ns() - start > p.limit_ns) {
                 ok = 0;  // a peer never arrived: give up, report, leave the output untouched
@@ -69,9 +79,7 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
         }
     }
     __syncthreads();
-    if (!ok)
-        return;
-    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < p.vectors;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; ok && i < p.vectors;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
         for (int r = 0; r < p.world; r++) {
@@ -91,23 +99,29 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
             oh[k] = __floats2half2_rn(sum[2 * k], sum[2 * k + 1]);
         p.out[i] = o;
     }
+    if (p.state != nullptr) {
+        // the last block to get here advances the epoch for the next launch
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            __threadfence();
+            if (atomicAdd(p.state + 1, 1u) == gridDim.x - 1) {
+                p.state[1] = 0;
+                __threadfence();
+                p.state[0] = epoch;
+            }
+        }
+    }
 }
 
 }  // namespace spmm_b200
 
-extern "C" int spmm_b200_allreduce_partials(void*              stream,
-                                            const void* const* partial_buffers,
-                                            void* const*       flag_arrays,
-                                            int                rank,
-                                            int                world,
-                                            void*              out,
-                                            size_t             count,
-                                            uint32_t           epoch,
-                                            unsigned           limit_ms)
+namespace spmm_b200 {
+namespace {
+int launch_allreduce(void* stream, const void* const* partial_buffers, void* const* flag_arrays, int rank, int world, void* out,
+                     size_t count, uint32_t epoch, uint32_t* state, unsigned limit_ms)
 {
-    using namespace spmm_b200;
     if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || count % 8 != 0 || !out || !partial_buffers
-        || !flag_arrays || epoch == 0)
+        || !flag_arrays || (epoch == 0 && state == nullptr))
         return static_cast<int>(cudaErrorInvalidValue);
     AllReduceParams p;
     for (int r = 0; r < world; r++) {
@@ -123,6 +137,7 @@ extern "C" int spmm_b200_allreduce_partials(void*              stream,
     p.rank     = rank;
     p.world    = world;
     p.epoch    = epoch;
+    p.state    = state;
     p.limit_ns = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
     const int blocks = static_cast<int>(p.vectors < 256 * 148 ? (p.vectors + 255) / 256 : 148);
     cudaLaunchConfig_t config = {};
@@ -136,6 +151,37 @@ extern "C" int spmm_b200_allreduce_partials(void*              stream,
     config.numAttrs                                    = 1;
     cudaError_t e = cudaLaunchKernelEx(&config, allreduce_partials_kernel, p);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
+}
+}  // namespace
+}  // namespace spmm_b200
+
+extern "C" int spmm_b200_allreduce_partials(void*              stream,
+                                            const void* const* partial_buffers,
+                                            void* const*       flag_arrays,
+                                            int                rank,
+                                            int                world,
+                                            void*              out,
+                                            size_t             count,
+                                            uint32_t           epoch,
+                                            unsigned           limit_ms)
+{
+    return spmm_b200::launch_allreduce(stream, partial_buffers, flag_arrays, rank, world, out, count, epoch, nullptr, limit_ms);
+}
+
+extern "C" int spmm_b200_allreduce_partials_replayable(void*              stream,
+                                                       const void* const* partial_buffers,
+                                                       void* const*       flag_arrays,
+                                                       int                rank,
+                                                       int                world,
+                                                       void*              out,
+                                                       size_t             count,
+                                                       void*              state,
+                                                       unsigned           limit_ms)
+{
+    if (state == nullptr || (reinterpret_cast<uintptr_t>(state) & 3u))
+        return static_cast<int>(cudaErrorInvalidValue);
+    return spmm_b200::launch_allreduce(stream, partial_buffers, flag_arrays, rank, world, out, count, 0,
+                                       static_cast<uint32_t*>(state), limit_ms);
 }
 
 extern "C" int spmm_b200_allreduce_status(int reset)

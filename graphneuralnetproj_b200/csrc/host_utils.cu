@@ -65,6 +65,22 @@ inline double unit_open(uint64_t x)
     return (static_cast<double>(x >> 11) + 0.5) * (1.0 / 9007199254740992.0);
 }
 
+// Element `index` of the stream spmm_b200_synth_fp16 draws: three counter-based uniforms per element.
+inline uint16_t synth_element(uint64_t index, uint64_t seed, double sigma, double p_zero)
+{
+    const uint64_t base = index * 3u;
+    const double   u3   = unit_open(splitmix64_at(seed, base + 2));
+    if (u3 < p_zero)
+        return 0;
+    const double u1 = unit_open(splitmix64_at(seed, base));
+    const double u2 = unit_open(splitmix64_at(seed, base + 1));
+    const double g  = std::sqrt(-2.0 * std::log(u1)) * std::cos(6.283185307179586476925 * u2);
+    const __half h  = __float2half_rn(static_cast<float>(sigma * g));
+    uint16_t     bits;
+    std::memcpy(&bits, &h, 2);
+    return bits;
+}
+
 }  // namespace
 
 // C++ entry points with the names and signatures of kernel_benchmark/spmm_decompose.h:12 and :53,
@@ -117,21 +133,18 @@ void spmm_b200_decompose_v1(const uint16_t* A, uint16_t* A1, uint16_t* A2, int l
 void spmm_b200_synth_fp16(uint16_t* out, long count, uint64_t seed, double sigma, double p_zero)
 {
     spmm_b200::parallel_for(count, [=](long i0, long i1) {
-        for (long i = i0; i < i1; i++) {
-            const uint64_t base = static_cast<uint64_t>(i) * 3u;
-            const double   u3   = unit_open(splitmix64_at(seed, base + 2));
-            if (u3 < p_zero) {
-                out[i] = 0;
-                continue;
-            }
-            const double u1 = unit_open(splitmix64_at(seed, base));
-            const double u2 = unit_open(splitmix64_at(seed, base + 1));
-            const double g  = std::sqrt(-2.0 * std::log(u1)) * std::cos(6.283185307179586476925 * u2);
-            const __half h  = __float2half_rn(static_cast<float>(sigma * g));
-            uint16_t     bits;
-            std::memcpy(&bits, &h, 2);
-            out[i] = bits;
-        }
+        for (long i = i0; i < i1; i++)
+            out[i] = synth_element(static_cast<uint64_t>(i), seed, sigma, p_zero);
+    });
+}
+
+void spmm_b200_synth_fp16_block(
+    uint16_t* out, long rows, long cols, long ld, long row0, long col0, uint64_t seed, double sigma, double p_zero)
+{
+    spmm_b200::parallel_for(rows, [=](long r0, long r1) {
+        for (long r = r0; r < r1; r++)
+            for (long c = 0; c < cols; c++)
+                out[r * cols + c] = synth_element(static_cast<uint64_t>((row0 + r) * ld + col0 + c), seed, sigma, p_zero);
     });
 }
 

@@ -2,6 +2,7 @@
 // SpMM_SplitK_Kernel_Ex (csrc/SpMM_API.cu:25-208), plus the extern "C" views
 // declared in include/spmm_b200.h.
 #include <algorithm>
+#include <atomic>
 #include <cmath>
 #include <cstdio>
 #include <cstring>
@@ -12,13 +13,6 @@
 #include "host_threads.h"
 #include "spmm_decode_kernel.cuh"
 #include "spmm_structured_kernel.cuh"
-
-#ifndef SPMM_B200_PFR
-#define SPMM_B200_PFR 2  // rounds ahead at which a team asks for its words to be brought into L2 (0 = never)
-#endif
-#ifndef SPMM_B200_ABL
-#define SPMM_B200_ABL 0  // experiment builds: ablation mask of spmm_decode_kernel (see its template parameters)
-#endif
 
 namespace spmm_b200 {
 namespace {
@@ -35,9 +29,13 @@ struct DecodeConfig {
     static constexpr int Q    = N <= 64 ? 4 : (N == 128 ? 2 : 1);  // MMA-issuing warps (2 * Q * N TMEM columns)
     static constexpr int VPL  = 14 / WPT;
     static constexpr int S    = N <= 64 ? 8 : (N == 128 ? 6 : 4);  // ring slots
-    static constexpr int BBUF = 1;                 // B buffers per ring slot
-    static constexpr int WTMA = N == 64 ? 0 : 1;   // words staged through shared memory by bulk copy
-    static constexpr int R    = D;  // staging buffers for the words: one per team (a shared ring of 9-11 measured slower)
+    // vectors per lane that are staged through shared memory by bulk copy (the rest are loaded straight
+    // into registers); none at N = 64, where staging buffers do not fit beside eight 16 KB A buffers
+    // and eight 8 KB B slices
+#ifndef SPMM_B200_VS16
+#define SPMM_B200_VS16 VPL
+#endif
+    static constexpr int VS   = N == 64 ? 0 : (N == 16 ? (SPMM_B200_VS16) : VPL);
     // B slices (row-major layout): tiled TMA loads, issued by the MMA warps a lap ahead into a second
     // B buffer where that fits in shared memory (N <= 16), else by the tile's decoder
     // (N = 8 keeps the 16-byte copies: its staged rows are twice as wide as the rows of B)
@@ -49,16 +47,41 @@ struct DeviceInfo {
     bool attrs_set[16] = {};  // cudaFuncSetAttribute done, per kernel instantiation
 };
 
+std::mutex g_device_lock;  // guards DeviceInfo, the workspace -> counter set table and the caches below
+
 DeviceInfo& device_info(int device)
 {
     static DeviceInfo info[64];
-    static std::mutex lock;
-    std::lock_guard<std::mutex> guard(lock);
+    std::lock_guard<std::mutex> guard(g_device_lock);
     DeviceInfo& d = info[device & 63];
     if (d.sm_count == 0)
         cudaDeviceGetAttribute(&d.sm_count, cudaDevAttrMultiProcessorCount, device);
     return d;
 }
+
+// Launches that may overlap in time must not share arrival counters.  Set 0 belongs to the launches
+// that park their partial tiles in the library's own scratch; every caller-provided workspace gets a
+// set of its own, remembered by its address (seven at a time per device; the least recently assigned
+// is handed on when an eighth workspace appears).
+int counter_set_for(int device, const void* workspace)
+{
+    static const void* owner[64][kCounterSets] = {};
+    static int         next[64]                = {};
+    if (workspace == nullptr)
+        return 0;
+    std::lock_guard<std::mutex> guard(g_device_lock);
+    const void** mine = owner[device & 63];
+    for (int i = 1; i < kCounterSets; i++)
+        if (mine[i] == workspace)
+            return i;
+    const int slot = 1 + (next[device & 63]++ % (kCounterSets - 1));
+    mine[slot]     = workspace;
+    return slot;
+}
+
+// Whether the weights may be fetched ahead of the stream predecessor's completion (see
+// spmm_b200_set_weights_constant).
+std::atomic<int> g_weights_constant{0};
 
 // Partition cache: the schedule depends only on the shape and the slot budget.
 struct PlanKey {
@@ -70,7 +93,8 @@ struct PlanKey {
     }
 };
 
-const Schedule& cached_schedule(const PlanKey& key)
+// Fills `out` (a copy: the cache entry may be replaced by another thread as soon as the lock is gone).
+void cached_schedule(const PlanKey& key, Schedule& out)
 {
     constexpr int   kEntries = 32;
     static PlanKey  keys[kEntries];
@@ -79,12 +103,14 @@ const Schedule& cached_schedule(const PlanKey& key)
     static std::mutex lock;
     std::lock_guard<std::mutex> guard(lock);
     for (int i = 0; i < used; i++)
-        if (keys[i] == key)
-            return plans[i];
+        if (keys[i] == key) {
+            out = plans[i];
+            return;
+        }
     const int slot = used < kEntries ? used++ : (next++ % kEntries);
     keys[slot]     = key;
     make_schedule(plans[slot], key.tiles_m, key.tiles_k, key.max_ctas, key.slots);
-    return plans[slot];
+    out = plans[slot];
 }
 
 template<int N, int TM = 0>
@@ -95,21 +121,23 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     using Cfg          = DecodeConfig<N>;
     constexpr int D    = Cfg::D;
     constexpr int BM   = TM ? 0 : Cfg::BM;  // token-major B keeps the 16-byte copies
-    constexpr int BBUF = BM == 2 ? 2 : Cfg::BBUF;
     constexpr int smem =
-        decode_smem_bytes<NB, Cfg::S, BBUF, Cfg::WTMA ? word_stage_bytes<Cfg::R, Cfg::WPT, Cfg::VPL>() : 0>();
+        decode_smem_bytes<NB, Cfg::S, BM, word_stage_bytes<D, Cfg::WPT, Cfg::VS>()>();
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, SPMM_B200_ABL, TM, BBUF, Cfg::S, Cfg::WTMA, SPMM_B200_PFR, Cfg::R, BM>;
-    if (!dev.attrs_set[n_index]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) {
-            (void)cudaGetLastError();  // do not leave the error behind for an unrelated later call
-            return e;
+    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, Cfg::S, TM, Cfg::VS, BM>;
+    {
+        std::lock_guard<std::mutex> guard(g_device_lock);
+        if (!dev.attrs_set[n_index]) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) {
+                (void)cudaGetLastError();  // do not leave the error behind for an unrelated later call
+                return e;
+            }
+            dev.attrs_set[n_index] = true;
         }
-        dev.attrs_set[n_index] = true;
     }
     // Launched so that it may start while the kernel before it in the stream drains (the kernel waits
-    // for its predecessor before touching anything but the weights).
+    // for its predecessor before touching anything it may still be working on).
     cudaLaunchConfig_t config = {};
     config.gridDim            = dim3(params.sched.num_ctas, column_blocks);
     config.blockDim           = dim3(decode_threads<D, Cfg::Q, Cfg::WPT>());
@@ -172,6 +200,24 @@ cudaError_t describe_b(CUtensorMap& map, const half* B, int N_Global, int K_Glob
             encode = reinterpret_cast<EncodeFn>(fn);
         }
     }
+    // the description depends only on (B, N, K, block width): callers multiply the same activations
+    // buffer again and again, so the last few descriptions are kept
+    struct Entry {
+        const half* B;
+        int         n, k, n_block;
+        CUtensorMap map;
+    };
+    constexpr int kEntries = 16;
+    static Entry  cache[kEntries];
+    static int    used = 0, next = 0;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        for (int i = 0; i < used; i++)
+            if (cache[i].B == B && cache[i].n == N_Global && cache[i].k == K_Global && cache[i].n_block == n_block) {
+                map = cache[i].map;
+                return cudaSuccess;
+            }
+    }
     const int                box_cols = n_block < 16 ? 16 : (n_block > 64 ? 64 : n_block);
     const CUtensorMapSwizzle swizzle  = box_cols == 16   ? CU_TENSOR_MAP_SWIZZLE_32B
                                         : box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B
@@ -184,6 +230,11 @@ cudaError_t describe_b(CUtensorMap& map, const half* B, int N_Global, int K_Glob
                CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
         != CUDA_SUCCESS)
         return cudaErrorInvalidValue;
+    {
+        std::lock_guard<std::mutex> guard(lock);
+        const int slot = used < kEntries ? used++ : (next++ % kEntries);
+        cache[slot]    = Entry{B, N_Global, K_Global, n_block, map};
+    }
     return cudaSuccess;
 }
 
@@ -241,30 +292,34 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.C            = C;
     params.slots        = reinterpret_cast<float*>(reinterpret_cast<char*>(Reduction_Workspace) + workspace_skip_bytes);
     long slots_granted  = slots;
+    params.counter_set  = counter_set_for(device, slots > 0 ? Reduction_Workspace : nullptr);
     if (!wide) {
         // A workspace sized by a small Split_K hint (the reference's 7168 x 7168 case passes 5) cannot
         // hold the partial tiles of a partition over all SMs; the library's built-in scratch takes its
         // place when it holds more.
-        const Schedule& all_sms = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, 1L << 40});
-        const long      own     = static_cast<long>(kOwnScratchBytes / (static_cast<size_t>(kTileRows) * n_block * sizeof(float)));
-        if (slots < all_sms.slots_used && own > slots) {
+        cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, 1L << 40}, params.sched);
+        const long own = static_cast<long>(kOwnScratchBytes / (static_cast<size_t>(kTileRows) * n_block * sizeof(float)));
+        if (slots < params.sched.slots_used && own > slots) {
             float* scratch = nullptr;
             if (own_scratch_address(device, &scratch) == cudaSuccess) {
-                params.slots  = scratch;
-                slots_granted = own;
+                params.slots       = scratch;
+                params.counter_set = 0;
+                slots_granted      = own;
             }
             else
                 (void)cudaGetLastError();
         }
     }
+    params.weights_early = g_weights_constant.load(std::memory_order_relaxed);
     params.addend       = addend;
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
     params.m            = M_Global;
     params.ld           = N_Global;
     // with several column blocks the blocks of one column share the SMs with the other columns
-    params.sched = cached_schedule(PlanKey{
-        tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count, slots_granted});
+    cached_schedule(PlanKey{tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count,
+                            slots_granted},
+                    params.sched);
     params.slots_per_block_column = params.sched.slots_used;
     if (!token_major && N_Global != 8) {
         e = describe_b(params.b_map, B, N_Global, K_Global, n_block);
@@ -312,13 +367,16 @@ cudaError_t launch_structured(cudaStream_t stream, DeviceInfo& dev, int n_index,
     constexpr int smem = structured_smem_bytes<NB, STAGES>();
     static_assert(smem <= 227 * 1024, "stages do not fit in shared memory");
     auto kern = spmm_structured_kernel<N, STAGES>;
-    if (!dev.attrs_set[n_index]) {
-        cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        if (e != cudaSuccess) {
-            (void)cudaGetLastError();
-            return e;
+    {
+        std::lock_guard<std::mutex> guard(g_device_lock);
+        if (!dev.attrs_set[n_index]) {
+            cudaError_t e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+            if (e != cudaSuccess) {
+                (void)cudaGetLastError();
+                return e;
+            }
+            dev.attrs_set[n_index] = true;
         }
-        dev.attrs_set[n_index] = true;
     }
     cudaLaunchConfig_t config = {};
     config.gridDim            = dim3(params.sched.num_ctas);
@@ -380,7 +438,9 @@ cudaError_t spmm_hetero(cudaStream_t stream, const half* values, const int* meta
     params.blocks_k = blocks_k;
     params.m        = M_Global;
     params.ld       = N_Global;
-    params.sched    = cached_schedule(PlanKey{tiles_m, blocks_k, dev.sm_count, slots});
+    params.counter_set   = counter_set_for(device, slots > 0 ? Reduction_Workspace : nullptr);
+    params.weights_early = g_weights_constant.load(std::memory_order_relaxed);
+    cached_schedule(PlanKey{tiles_m, blocks_k, dev.sm_count, slots}, params.sched);
     switch (N_Global) {
         case 8:
             e = launch_structured<8, 9>(stream, dev, 8, params);
@@ -482,7 +542,8 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
     const size_t slot_bytes = static_cast<size_t>(kTileRows) * N_Global * sizeof(float);
     // The balanced partition over all SMs must fit: its partial tiles are what the scratch is for.
     Schedule full;
-    fill_schedule(full, tiles_m, tiles_k, static_cast<int>(total < dev.sm_count ? total : dev.sm_count), 1);
+    const int full_ctas = std::min(dev.sm_count, kMaxCtas);
+    fill_schedule(full, tiles_m, tiles_k, static_cast<int>(total < full_ctas ? total : full_ctas), 1);
     if (static_cast<size_t>(full.slots_used) * slot_bytes > kOwnScratchBytes) {
         printf("spmm_b200_spmm_own_scratch: this shape needs %zu bytes of scratch, the built-in array holds %zu\n",
                static_cast<size_t>(full.slots_used) * slot_bytes, kOwnScratchBytes);
@@ -508,7 +569,9 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
         if (e != cudaSuccess)
             return static_cast<int>(e);
     }
-    params.sched = cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, static_cast<long>(kOwnScratchBytes / slot_bytes)});
+    params.counter_set   = 0;
+    params.weights_early = g_weights_constant.load(std::memory_order_relaxed);
+    cached_schedule(PlanKey{tiles_m, tiles_k, dev.sm_count, static_cast<long>(kOwnScratchBytes / slot_bytes)}, params.sched);
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     switch (N_Global) {
         case 8:
@@ -524,19 +587,6 @@ extern "C" int spmm_b200_spmm_own_scratch(void*       stream,
 
 // ------------------------------------------------------------------ extern "C"
 extern "C" {
-#ifdef SPMM_B200_ABLATIONS
-int spmm_b200_debug_trace(unsigned long long* out)
-{
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, spmm_b200::g_trace, sizeof(unsigned long long) * 320 * 16);
-}
-int spmm_b200_debug_fine(long long* out)
-{
-    cudaDeviceSynchronize();
-    return (int)cudaMemcpyFromSymbol(out, spmm_b200::g_fine, sizeof(long long) * 320 * 32);
-}
-#endif
-
 int spmm_b200_init_sparse_matrix_a(const uint16_t* A_h, int M, int N, int K, uint32_t** Compressed_A, int** TileOffsets)
 {
     if (M <= 0 || K <= 0 || M % 128 != 0 || K % 64 != 0)
@@ -616,6 +666,97 @@ int spmm_b200_spmm_splitk_host_io(void*       stream,
                                             cudaMemcpyDeviceToHost, st));
 }
 
+namespace spmm_b200 {
+namespace {
+// Copy streams and events of spmm_b200_spmm_splitk_host_io_batch, created on first use, one set per device.
+struct HostIoLanes {
+    bool         ready = false;
+    cudaStream_t in = nullptr, out = nullptr;
+    cudaEvent_t  fork = nullptr, joined = nullptr;
+    cudaEvent_t  landed[SPMM_B200_HOST_IO_MAX_ITEMS] = {};
+    cudaEvent_t  multiplied[SPMM_B200_HOST_IO_MAX_ITEMS] = {};
+};
+std::mutex  g_host_io_lock;
+HostIoLanes g_host_io_lanes[64];
+
+cudaError_t host_io_lanes(int device, HostIoLanes** out)
+{
+    HostIoLanes& lanes = g_host_io_lanes[device & 63];
+    if (!lanes.ready) {
+        cudaError_t e = cudaStreamCreateWithFlags(&lanes.in, cudaStreamNonBlocking);
+        if (e == cudaSuccess)
+            e = cudaStreamCreateWithFlags(&lanes.out, cudaStreamNonBlocking);
+        if (e == cudaSuccess)
+            e = cudaEventCreateWithFlags(&lanes.fork, cudaEventDisableTiming);
+        if (e == cudaSuccess)
+            e = cudaEventCreateWithFlags(&lanes.joined, cudaEventDisableTiming);
+        for (int i = 0; i < SPMM_B200_HOST_IO_MAX_ITEMS && e == cudaSuccess; i++) {
+            e = cudaEventCreateWithFlags(&lanes.landed[i], cudaEventDisableTiming);
+            if (e == cudaSuccess)
+                e = cudaEventCreateWithFlags(&lanes.multiplied[i], cudaEventDisableTiming);
+        }
+        if (e != cudaSuccess)
+            return e;
+        lanes.ready = true;
+    }
+    *out = &lanes;
+    return cudaSuccess;
+}
+}  // namespace
+}  // namespace spmm_b200
+
+int spmm_b200_spmm_splitk_host_io_batch(void* stream, int count, const spmm_b200_host_io_item* items)
+{
+    using namespace spmm_b200;
+    if (count < 1 || count > SPMM_B200_HOST_IO_MAX_ITEMS || !items)
+        return static_cast<int>(cudaErrorInvalidValue);
+    for (int i = 0; i < count; i++)
+        if (!items[i].B_host || !items[i].C_host || !items[i].B_dev || !items[i].C_dev || items[i].M <= 0 || items[i].N <= 0
+            || items[i].K <= 0)
+            return static_cast<int>(cudaErrorInvalidValue);
+    int         device = 0;
+    cudaError_t e      = cudaGetDevice(&device);
+    if (e != cudaSuccess)
+        return static_cast<int>(e);
+    std::lock_guard<std::mutex> guard(g_host_io_lock);
+    HostIoLanes* lanes = nullptr;
+    e = host_io_lanes(device, &lanes);
+    if (e != cudaSuccess)
+        return static_cast<int>(e);
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+#define SPMM_B200_TRY(call)                \
+    do {                                   \
+        e = (call);                        \
+        if (e != cudaSuccess)              \
+            return static_cast<int>(e);    \
+    } while (0)
+    // the copies start once everything queued on `stream` so far has finished with the buffers
+    SPMM_B200_TRY(cudaEventRecord(lanes->fork, st));
+    SPMM_B200_TRY(cudaStreamWaitEvent(lanes->in, lanes->fork, 0));
+    SPMM_B200_TRY(cudaStreamWaitEvent(lanes->out, lanes->fork, 0));
+    for (int i = 0; i < count; i++) {
+        const spmm_b200_host_io_item& it = items[i];
+        SPMM_B200_TRY(cudaMemcpyAsync(it.B_dev, it.B_host, static_cast<size_t>(it.K) * it.N * sizeof(half),
+                                      cudaMemcpyHostToDevice, lanes->in));
+        SPMM_B200_TRY(cudaEventRecord(lanes->landed[i], lanes->in));
+    }
+    for (int i = 0; i < count; i++) {
+        const spmm_b200_host_io_item& it = items[i];
+        SPMM_B200_TRY(cudaStreamWaitEvent(st, lanes->landed[i], 0));
+        SPMM_B200_TRY(SpMM_SplitK_API(st, nullptr, static_cast<const uint4*>(it.Compressed_A), nullptr, nullptr, it.TileOffsets,
+                                      static_cast<const half*>(it.B_dev), static_cast<half*>(it.C_dev), it.M, it.N, it.K,
+                                      static_cast<half*>(it.Reduction_Workspace), it.Split_K));
+        SPMM_B200_TRY(cudaEventRecord(lanes->multiplied[i], st));
+        SPMM_B200_TRY(cudaStreamWaitEvent(lanes->out, lanes->multiplied[i], 0));
+        SPMM_B200_TRY(cudaMemcpyAsync(it.C_host, it.C_dev, static_cast<size_t>(it.M) * it.N * sizeof(half),
+                                      cudaMemcpyDeviceToHost, lanes->out));
+    }
+    SPMM_B200_TRY(cudaEventRecord(lanes->joined, lanes->out));
+    SPMM_B200_TRY(cudaStreamWaitEvent(st, lanes->joined, 0));
+#undef SPMM_B200_TRY
+    return static_cast<int>(cudaSuccess);
+}
+
 int spmm_b200_spmm_splitk_token_major(void*       stream,
                                       const void* Compressed_A,
                                       const int*  TileOffsets,
@@ -631,6 +772,11 @@ int spmm_b200_spmm_splitk_token_major(void*       stream,
                                             static_cast<const uint4*>(Compressed_A), TileOffsets,
                                             static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global,
                                             K_Global, static_cast<half*>(Reduction_Workspace), Split_K));
+}
+
+int spmm_b200_set_weights_constant(int constant)
+{
+    return spmm_b200::g_weights_constant.exchange(constant ? 1 : 0);
 }
 
 size_t spmm_b200_workspace_bytes(int M_Global, int N_Global, int Split_K)
@@ -652,7 +798,7 @@ int spmm_b200_device_status(int reset)
         cudaMemcpyToSymbol(spmm_b200::g_device_status, &zero, sizeof(int));
         void* counters = nullptr;
         if (cudaGetSymbolAddress(&counters, spmm_b200::g_row_arrivals) == cudaSuccess)
-            cudaMemset(counters, 0, sizeof(unsigned int) * spmm_b200::kMaxRowTiles * spmm_b200::kEpilogueWarps);
+            cudaMemset(counters, 0, sizeof(spmm_b200::g_row_arrivals));
         cudaDeviceSynchronize();
     }
     return status;

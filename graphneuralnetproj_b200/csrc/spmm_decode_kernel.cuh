@@ -1,4 +1,5 @@
-// Decode-size (N <= 64) "load-as-sparse, compute-as-dense" SpMM for sm_100a.
+// "Load-as-sparse, compute-as-dense" SpMM for sm_100a: C[M][N] = A * B with A in the reference's
+// tiled-CSL format (128 x 64 tiles of value|position words, csrc/SpMM_API.cu:241-438).
 //
 // Replaces the reference's SpMM_Kernel (csrc/SpMM_Kernel.cuh:293-735) and its
 // Ampere pipeline -- cp.async staging, ldmatrix, mma.sync m16n8k16
@@ -6,41 +7,48 @@
 // the split-K reduction (csrc/Reduction_Kernel.cuh:24-47) into the epilogue.
 //
 // One persistent thread block per SM works through a contiguous chunk of the
-// tile sequence (see schedule.h).  Roles, by warp:
+// tile sequence (see schedule.h).  The block keeps a ring of S slots, each a
+// 16 KB buffer for a restored 128 x 64 fp16 tile of A plus one or two staged
+// 64 x N slices of B.  Roles, by warp:
 //
-//   warps 0..3   epilogue: TMEM -> registers -> C, or -> an fp32 slot plus the
-//                last-arriver reduction for rows whose K range is shared
+//   warps 0..3      epilogue: TMEM -> registers -> C, or -> an fp32 slot plus the
+//                   last-arriver reduction for rows whose K range is shared
 //   warps 4..4+Q-1  MMA issue: one lane each; warp q takes tiles q, q + Q, ... of the
-//                chunk and accumulates them in its own TMEM accumulator (the
-//                epilogue adds the Q accumulators in a fixed order).  Several
-//                issuers because one lane, sharing its scheduler with busy
-//                decoder warps, cannot issue four MMAs and a commit per tile fast
-//                enough; warp 4 also allocates TMEM
-//   warps 4+Q..  decoders.  The block keeps a ring of D tile buffers (16 KB of
-//                restored A plus two staged B slices each); buffer s is owned by
-//                a team of WPT warps that handles tiles s, s + D, s + 2D, ... of
-//                the chunk.  Per tile a team
-//                  - streams the tile's words into registers with 128-bit loads
-//                    (issued one tile ahead, right after the previous scatter),
-//                  - waits until the tensor core has finished with the buffer,
-//                  - clears the buffer with 128-bit stores,
-//                  - scatters the values to the half-word positions the words carry,
-//                  - issues the copy of its next tile's B slice, and hands the
-//                    buffer to an MMA lane.
+//                   chunk and accumulates them in its own TMEM accumulator (the
+//                   epilogue adds the Q accumulators in a fixed order).  Several
+//                   issuers because one lane, sharing its scheduler with busy
+//                   decoder warps, cannot issue four MMAs and a commit per tile fast
+//                   enough; warp 4 also allocates TMEM.  Where B arrives by tiled TMA
+//                   loads a lap ahead (BM == 2) these lanes issue them, and they ask
+//                   for the words two laps ahead to be brought into L2.
+//   warps 4+Q..     decoders: D teams of WPT warps; team t restores tiles t, t + D, ...
+//                   of the chunk into slot (tile % S).  Per tile a team
+//                     - receives the first part of the tile's words in its staging buffer
+//                       (one bulk copy, issued a whole tile ahead, completion on an
+//                       mbarrier) and reads them into registers; the buffer goes back to
+//                       the copy engine at once for the team's next tile; the rest of the
+//                       words come by 128-bit streaming loads straight into registers,
+//                       issued as soon as the previous tile has been scattered,
+//                     - waits until the tensor core has finished with the slot,
+//                     - clears the A buffer with 128-bit stores,
+//                     - scatters the values to the half-word positions the words carry,
+//                     - hands the slot to an MMA lane (mbarrier arrive).
 //
 // The position stored in each word, row * 64 + (col ^ ((row % 8) << 3))
 // (csrc/SpMM_API.cu:330-339), is the element offset of (row, col) in a K-major
 // 128 x 64 fp16 tile in the tensor core's 128-byte-swizzle layout, so the
 // scatter needs no index arithmetic and the restored tile is read by
 // tcgen05.mma as it lies.  B[K][N] is row-major, i.e. N-contiguous ("MN-major"
-// for the tensor core); a 64 x N slice is copied chunk by chunk into the
-// matching 32/64/128-byte-swizzle layout.  Accumulation is fp32 in TMEM, two
-// accumulators so that the epilogue of one row of tiles overlaps the next.
+// for the tensor core); a 64 x N slice is staged in the matching 32/64/128-byte
+// swizzle layout.  Accumulation is fp32 in TMEM, two accumulator sets so that
+// the epilogue of one row of tiles overlaps the next.
 //
 // Every wait is bounded (ptx::mbar_wait_bounded); a wait that gives up raises
 // a block-wide abort word, all roles fall through to the common exit, TMEM is
 // released and a status word in global memory records the event.
 #pragma once
+
+#include <type_traits>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -55,31 +63,17 @@ constexpr int kTileCols        = 64;   // k extent of an encoded tile
 constexpr int kATileBytes      = kTileRows * kTileCols * 2;
 constexpr int kEpilogueWarps   = 4;
 constexpr int kFirstMmaWarp    = 4;
-constexpr int kMaxRowTiles     = 32768;  // arrival counters: rows of tiles x 64-column blocks per launch
+constexpr int kMaxRowTiles     = 32768;  // arrival counters: rows of tiles x column blocks per launch
+constexpr int kCounterSets     = 8;      // independent sets of arrival counters (one per workspace in use)
+constexpr int kPrefetchRounds  = 2;      // a tile's words are asked into L2 this many laps before they are copied
 
-enum DeviceStatus : int { kStatusOk = 0, kStatusWaitTimeout = 1 };
+enum DeviceStatus : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadInput = 2 };
 
 // Arrival counters for rows of tiles whose K range is split between blocks, four per
 // row (one per 32-row quarter, i.e. per epilogue warp).  Zero between launches: the
-// last arriver resets its counter.
-__device__ unsigned int g_row_arrivals[kMaxRowTiles * kEpilogueWarps];
+// last arriver resets its counter.  Launches that may overlap in time use different sets.
+__device__ unsigned int g_row_arrivals[kCounterSets][kMaxRowTiles * kEpilogueWarps];
 __device__ int          g_device_status;
-
-#ifdef SPMM_B200_ABLATIONS
-__device__ unsigned long long g_trace[320 * 16];
-__device__ long long          g_fine[320 * 32];
-__device__ __forceinline__ long long fine_clock()
-{
-    long long c;
-    asm volatile("mov.u64 %0, %%clock64;" : "=l"(c));
-    return c;
-}
-#define SPMM_TRACE(slot) do { if (lane == 0) g_trace[blockIdx.x * 16 + (slot)] = ptx::global_timer_ns(); } while (0)
-#define SPMM_FINE(cond, slot) do { if ((cond) && lane == 0) g_fine[blockIdx.x * 32 + (slot)] = fine_clock(); } while (0)
-#else
-#define SPMM_TRACE(slot) do { } while (0)
-#define SPMM_FINE(cond, slot) do { } while (0)
-#endif
 
 struct DecodeParams {
     const uint4* words        = nullptr;  // tiled-CSL words, viewed as 4-word vectors
@@ -87,14 +81,19 @@ struct DecodeParams {
     const half*  B            = nullptr;  // [K][N] row-major
     half*        C            = nullptr;  // [M][N] row-major
     float*       slots        = nullptr;  // fp32 partial tiles, 128 * N floats each
+    int          counter_set  = 0;        // which set of arrival counters this launch uses
     int          n            = 0;        // N (8, 16, 32 or 64)
     int          tiles_k      = 0;        // K / 64
     int          m            = 0;        // M
     int          ld           = 0;  // row stride of B[K][ld] and C[M][ld] in halves (row-major layout): the full N
     int          slots_per_block_column = 0;  // workspace slots used by one column block (blockIdx.y)
+    // 1: the weights and their offsets were complete before the kernel ahead of this one in the stream
+    // started (constant inference weights), so they may be fetched before that kernel has finished;
+    // 0: nothing is read before the stream predecessor has completed
+    int          weights_early = 0;
     const float* addend = nullptr;  // optional fp32 [M][N] added before the rounding (row-major results, N <= 64 only)
-    // B as a 2-D tensor [K][ld] of halves with a 64 x 64 box and 128-byte swizzle: used by the 128- and
-    // 256-column forms, whose B slices arrive by tiled TMA loads instead of 16-byte copies
+    // B as a 2-D tensor [K][ld] of halves, boxes of 64 k rows x min(N, 64) columns in the swizzle mode of
+    // the staged layout: for the forms whose B slices arrive by tiled TMA loads (BM != 0)
     alignas(64) CUtensorMap b_map;
     Schedule     sched;
 };
@@ -129,17 +128,17 @@ struct BTile {
 
 // Per ring slot one A buffer and BBUF B buffers; STAGE bytes of word staging buffers (0 when the
 // words are loaded straight into registers).
-template<int NB, int S, int BBUF = 2, int STAGE = 0>
+template<int NB, int S, int BM, int STAGE>
 constexpr int decode_smem_bytes()
 {
-    return 1024 + S * (kATileBytes + BBUF * BTile<NB>::kBytes) + STAGE + 512;
+    return 1024 + S * (kATileBytes + (BM == 2 ? 2 : 1) * BTile<NB>::kBytes) + STAGE + 512;
 }
 
-// Staging bytes for D decoder teams that each hold WPT * VPL * 32 vectors of 16 bytes.
-template<int D, int WPT, int VPL>
+// Staging bytes for D decoder teams that each stage WPT * VS * 32 vectors of 16 bytes.
+template<int D, int WPT, int VS>
 constexpr int word_stage_bytes()
 {
-    return D * WPT * VPL * 32 * 16;
+    return D * WPT * VS * 32 * 16;
 }
 
 template<int D, int Q, int WPT>
@@ -166,63 +165,65 @@ __device__ __forceinline__ bool warp_wait(uint32_t bar, uint32_t parity, volatil
     return __shfl_sync(0xffffffffu, ok, 0) != 0;
 }
 
-// N   : columns of B / C (8, 16, 32, 64);   NB : columns of the staged B tile (16 when N == 8)
-// D   : decoder teams;  Q : MMA-issuing warps;  WPT : decoder warps per team;
-// VPL : 4-word vectors held per lane
-// S   : slots of the tile ring (0 = D).  Tile l of the chunk is decoded by team l % D into slot l % S
-//       and multiplied by MMA warp l % Q.  With S > D a team moves on to a slot whose previous MMA
-//       was issued S - D tiles earlier, instead of waiting out the round trip of its own last tile.
-// WTMA : 1 = a tile's words travel global -> shared memory by bulk copy (one staging buffer per
-//       team, completion on an mbarrier) and are then read into registers, instead of being loaded
-//       into registers directly.  Register loads are tracked in L1, whose size (what the shared
-//       memory carve-out leaves) then bounds the bytes in flight; the copy engine has no such bound.
-// PFR : a team asks for the words of its tile PFR rounds ahead (tile l + PFR * D) to be brought into L2
-//       (0 = no such requests).
-// R   : staging buffers for the words (WTMA; 0 = D).  Tile l of the chunk lands in buffer l % R; the
-//       team that has just emptied a buffer (tile l) asks for tile l + R into it, so R tiles are in
-//       flight per block whichever team will consume them.  The copy of a tile is then issued R
-//       tiles, not one round of D tiles, before it is needed.
-// BM  : how a tile's B slice reaches shared memory.  0: 16-byte async copies by the decoders;
-//       1: tiled TMA loads issued by the tile's decoder after the slot has been handed back;
-//       2: tiled TMA loads issued by the MMA warp one lap ahead into the other of two B buffers
-//       (the decoders never touch B; needs BBUF == 2).  1 and 2 need p.b_map and row-major B.
-// BBUF : B buffers per slot.  2: the next tile's slice is fetched while this one is decoded (needs
-//       S == D); 1: the slice is fetched after the slot has been handed back.
-// ABL : debugging ablation mask (0 in production): 1 no clearing, 2 no scatter, 4 no word loads,
-//       8 no MMA, 16 no B copy
-// TM : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
-//      library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
-//      k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
-template<int N, int D, int Q, int WPT, int VPL, int ABL = 0, int TM = 0, int BBUF = 2, int S_ = 0, int WTMA = 0, int PFR = 2, int R_ = 0, int BM = 0>
+// The value of each of the four words of `w` goes to the half-word position the word carries, in the
+// tile at `tile` (a pointer into shared memory).  Written as plain stores so that the compiler hoists
+// the address arithmetic of all vectors of a tile and predicates the stores of a ragged last group:
+// measured on one warp, 4.3 cycles per store against 12.9 for the same stores inside a branch per vector.
+// Positions are taken modulo the tile (13 bits), so a corrupt word cannot write outside the buffer.
+__device__ __forceinline__ void scatter_vector(uint8_t* tile, const uint4& w, bool valid)
+{
+    if (valid) {
+        *reinterpret_cast<uint16_t*>(tile + ((w.x >> 15) & 0x3ffeu)) = static_cast<uint16_t>(w.x);
+        *reinterpret_cast<uint16_t*>(tile + ((w.y >> 15) & 0x3ffeu)) = static_cast<uint16_t>(w.y);
+        *reinterpret_cast<uint16_t*>(tile + ((w.z >> 15) & 0x3ffeu)) = static_cast<uint16_t>(w.z);
+        *reinterpret_cast<uint16_t*>(tile + ((w.w >> 15) & 0x3ffeu)) = static_cast<uint16_t>(w.w);
+    }
+}
+
+// N    : columns of B / C handled by one block column (8, 16, 32, 64, 128, 256); the staged B tile has
+//        NB = max(N, 16) columns
+// D    : decoder teams;  Q : MMA-issuing warps;  WPT : decoder warps per team;
+// VPL  : 4-word vectors held per lane;  S : ring slots (S >= D, S % Q == 0).  Tile l of the chunk is
+//        decoded by team l % D into slot l % S and multiplied by MMA warp l % Q.
+// TM   : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
+//        library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
+//        k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
+// VS   : how many of a lane's VPL vectors travel global -> shared memory by bulk copy (one staging
+//        buffer of VS * WPT * 32 vectors per team) and are then read into registers; the other
+//        VPL - VS are 128-bit streaming loads straight into registers, issued a tile ahead.
+//        Register loads are tracked in L1, whose size (what the shared memory carve-out leaves) bounds
+//        their bytes in flight; bulk copies have no such bound but the copy engine moves only about
+//        25 bytes per clock into an SM's shared memory.  Splitting a tile between the two paths uses both.
+// BM   : how a tile's B slice reaches shared memory.  0: 16-byte async copies by the tile's decoders,
+//        1: tiled TMA loads issued by one of them, both once the slot has been handed back (one B
+//        buffer per slot); 2: tiled TMA loads issued by the MMA warp one lap ahead into the other of
+//        two B buffers per slot (the decoders never touch B).  1 and 2 need p.b_map and row-major B.
+template<int N, int D, int Q, int WPT, int VPL, int S, int TM, int VS, int BM>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
-    constexpr int NB = N < 16 ? 16 : N;
-    constexpr int S  = S_ == 0 ? D : S_;
-    constexpr int R  = R_ == 0 ? D : R_;
-    static_assert(R >= D, "every team starts with a staged tile of its own");
-    using BT         = BTile<NB>;
+    constexpr int NB   = N < 16 ? 16 : N;
+    constexpr int BBUF = BM == 2 ? 2 : 1;  // B buffers per slot
+    using BT           = BTile<NB>;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base    = smem_base;
     const uint32_t b_base    = a_base + S * kATileBytes;
     const uint32_t w_base    = b_base + BBUF * S * BT::kBytes;  // word staging, one buffer per team
-    constexpr int  kStageBytes = WPT * VPL * 32 * 16;
-    const uint32_t bar_base  = w_base + (WTMA ? R * kStageBytes : 0);
-    // barrier map (8 bytes each): [0,S) tile full, [S,2S) tile free, then acc full x2, acc free x2
-    auto tile_full = [&](int s) { return bar_base + 8u * s; };
-    auto tile_free = [&](int s) { return bar_base + 8u * (S + s); };
-    auto acc_full  = [&](int b) { return bar_base + 8u * (2 * S + b); };
-    auto acc_free  = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
+    constexpr bool WTMA        = VS > 0;
+    constexpr int  kStageBytes = WPT * VS * 32 * 16;
+    static_assert(VS >= 0 && VS <= VPL, "a lane cannot stage more vectors than it holds");
+    const uint32_t bar_base  = w_base + D * kStageBytes;
+    // barrier map (8 bytes each): [0,S) tile full, [S,2S) tile free, acc full x2, acc free x2, [.., +D) words full
+    auto tile_full  = [&](int s) { return bar_base + 8u * s; };
+    auto tile_free  = [&](int s) { return bar_base + 8u * (S + s); };
+    auto acc_full   = [&](int b) { return bar_base + 8u * (2 * S + b); };
+    auto acc_free   = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
     auto words_full = [&](int t) { return bar_base + 8u * (2 * S + 4 + t); };
-    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4 + R);
+    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4 + D);
     uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
     volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
-    // rounds[b]: how many times staging buffer b has been handed back to the copy engine.  A team may
-    // reach its wait for tile l before the previous tile of that buffer has even landed; the barrier's
-    // parity cannot tell those two phases apart, this counter can.
-    volatile uint32_t* rounds = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr + 8 - smem_base));
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -233,33 +234,31 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const int num_tiles  = tile_end - tile_begin;
     const int tiles_k    = p.tiles_k;
     constexpr int      kFirstDecodeWarp = kFirstMmaWarp + Q;
-    // Who asks for the words PFR laps ahead to be brought into L2: the MMA warps (which have time to
-    // spare) wherever the kernel uses the tensor-map forms of loading B, else the decoders.
+    // Who asks for the words kPrefetchRounds laps ahead to be brought into L2: the MMA warps (which have
+    // time to spare) wherever the kernel uses the tensor-map forms of loading B, else the decoders.
     constexpr bool     kMmaRequests     = BM != 0;
     constexpr uint32_t kTmemCols        = tmem_columns(2 * Q * NB);  // accumulator (q, b) at column (b * Q + q) * NB
     static_assert(2 * Q * NB <= 512, "accumulators exceed the 512 TMEM columns");
     static_assert(S % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
     static_assert(S >= D, "every team needs a slot of its own to start with");
-    static_assert(BBUF == 1 || S == D, "fetching the next B slice early needs a slot that stays with its team");
-    static_assert(8 * (2 * S + 4 + R) + 8 + 4 * R <= 512, "barrier block");
+    static_assert(BM == 0 || !TM, "tiled loads of B are for the row-major layout");
+    static_assert(8 * (2 * S + 4 + D) + 8 <= 512, "barrier block");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             ptx::mbar_init(tile_full(s), WPT);
             ptx::mbar_init(tile_free(s), 1);
         }
-        for (int t = 0; t < R; t++)
+        for (int t = 0; t < D; t++)
             ptx::mbar_init(words_full(t), 1);
         for (int b = 0; b < 2; b++) {
             ptx::mbar_init(acc_full(b), Q);
             ptx::mbar_init(acc_free(b), kEpilogueWarps);
         }
         *abort_word = 0;
-        for (int t = 0; t < R; t++)
-            rounds[t] = 0;
         ptx::mbar_init_fence();
     }
-    // Clear the ring once: A buffers are kept all-zero between tiles, and columns N..NB-1 of the
+    // Clear the ring once: the first lap scatters into it as it is, and columns N..NB-1 of the
     // staged B slices (N == 8) are never written.
     for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(S * (kATileBytes + BBUF * BT::kBytes));
          off += blockDim.x * 16u)
@@ -272,14 +271,11 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     __syncthreads();
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    if (warp == 0)
-        SPMM_TRACE(0);  // prologue done
     // Programmatic dependent launch: the next kernel in the stream may be scheduled from here on (it
     // still needs this block's resources to start on this SM).  This kernel in turn may have started
     // before its predecessor finished: everything the predecessor may still be writing or reading --
-    // B, C, the workspace, the arrival counters -- is touched only after ptx::grid_dependency_wait();
-    // the weights and their offsets are not covered by that rule (they are constant during inference)
-    // and are requested before the wait.
+    // B, C, the workspace, the arrival counters, and unless p.weights_early is set the weights and
+    // their offsets too -- is touched only after ptx::grid_dependency_wait().
     ptx::grid_launch_dependents();
 
     if (warp >= kFirstDecodeWarp) {
@@ -287,27 +283,22 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         const int s_own = (warp - kFirstDecodeWarp) / WPT;  // this team; also its first tile and first slot
         const int h     = (warp - kFirstDecodeWarp) % WPT;  // this warp's share of the tile
         uint32_t  slot  = s_own;                            // ring slot of the tile being decoded
-        uint32_t  a_tile = a_base + slot * kATileBytes;
         auto team_sync = [&]() {
             if (WPT > 1)
                 asm volatile("bar.sync %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
             else
                 __syncwarp();
         };
-        // B staging: a 64 x N slice is kTileCols * N / 8 chunks of 16 bytes, contiguous in global
-        // memory; this warp copies chunks first_chunk, first_chunk + WPT * 32, ...  Chunk c lands at
-        // swizzle(row * row_bytes + col * 16) with row = c / chunks_per_row, col = c % chunks_per_row.
-        constexpr bool kBTma        = BM == 1;
-        static_assert(!kBTma || BBUF == 1, "tiled loads of B by the decoder go to the slot's only B buffer");
-        static_assert(BM == 0 || !TM, "tiled loads of B are for the row-major layout");
-        static_assert(BM != 2 || (BBUF == 2 && Q > 0), "loads of B issued by the MMA warps use two B buffers");
+        // B staging by the decoders (BM == 0): a 64 x N slice is kTileCols * N / 8 chunks of 16 bytes,
+        // contiguous in global memory; this warp copies chunks first_chunk, first_chunk + WPT * 32, ...
+        // Chunk c lands at swizzle(row * row_bytes + col * 16), row = c / chunks_per_row.
         constexpr int kChunksPerRow = N / 8;
         constexpr int kChunks       = kTileCols * kChunksPerRow;
         const int     first_chunk   = h * 32 + lane;
-        auto stage_b = [&](int j, int parity) {
-            if ((ABL & 16) || BM == 2)
+        auto stage_b = [&](int j) {
+            if (BM == 2)
                 return;
-            if (kBTma) {
+            if (BM == 1) {
                 // one box of 64 k rows x 64 columns per swizzle atom; the bytes are counted on the
                 // barrier the MMA warp waits on for this tile
                 if (h == 0 && lane == 0) {
@@ -320,7 +311,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 }
                 return;
             }
-            const uint32_t dst = b_base + ((BBUF == 2 ? parity : 0) * S + slot) * BT::kBytes;
+            const uint32_t dst = b_base + slot * BT::kBytes;
             if (TM) {
                 // row n of the slice: 64 halves of token n starting at column 64 j (eight 16-byte chunks);
                 // chunk q of row n lands at n * 128 + ((q ^ (n % 8)) * 16)
@@ -340,90 +331,81 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             for (int i = 0; i < kChunks / (WPT * 32); i++) {
                 const uint32_t c   = first_chunk + i * WPT * 32;
                 const uint32_t row = c / kChunksPerRow, col = c % kChunksPerRow;
-                ptx::cp_async_16(dst + BT::offset(row, col),
-                                 b_src + static_cast<size_t>(row) * p.ld + col * 8);
+                ptx::cp_async_16(dst + BT::offset(row, col), b_src + static_cast<size_t>(row) * p.ld + col * 8);
             }
         };
-        auto zero_a = [&]() {
-#pragma unroll
-            for (int i = h; i < kATileBytes / (32 * 16); i += WPT)
-                ptx::st_shared_zero_128(a_tile + lane * 16u + i * 512u);
-        };
         // Vector v of this lane within a tile: teams interleave their warps by groups of 32 vectors.
-        const int lane_vec = h * 32 + lane;
-        uint4     r[VPL];  // this warp's share of the tile's words
-        int       nvec = 0, next0 = 0, next1 = 0;
-        int       j    = (tile_begin + s_own) % tiles_k;
-        auto load_words = [&](const uint4* from, int count) {
+        const int    lane_vec = h * 32 + lane;
+        constexpr int kBatch  = VPL * WPT * 32;  // vectors a team holds in registers at a time
+        uint4        r[VPL];                     // this warp's share of the tile's words
+        int          nvec = 0, next0 = 0, next1 = 0;
+        int          j    = (tile_begin + s_own) % tiles_k;
+        // Register loads of vectors V0 .. VPL - 1 of this lane from `from` (this lane's vector 0 of the
+        // batch).  No branch per load (loads inside branches do not pipeline): a lane whose vector lies
+        // beyond the batch's `count` reads the batch's last vector instead and never scatters it.
+        auto load_words = [&](const uint4* from, int count, auto first_vector) {
+            constexpr int V0 = decltype(first_vector)::value;
+            if (count <= 0)
+                return;
+#pragma unroll
+            for (int v = V0; v < VPL; v++)
+                r[v] = ptx::ld_stream_128(from + (min(lane_vec + v * WPT * 32, count - 1) - lane_vec));
+        };
+        using FromVector0  = std::integral_constant<int, 0>;
+        using FromVectorVS = std::integral_constant<int, VS>;
+        auto scatter_batch = [&](uint8_t* tile, int count) {
 #pragma unroll
             for (int v = 0; v < VPL; v++)
-                if (lane_vec + v * WPT * 32 < count) {
-                    if (ABL & 4)
-                        r[v] = make_uint4(lane << 17, (lane + 32) << 17, (lane + 64) << 17, (lane + 96) << 17);
-                    else
-                        r[v] = ptx::ld_stream_128(from + v * WPT * 32);
-                }
+                scatter_vector(tile, r[v], lane_vec + v * WPT * 32 < count);
         };
-        // WTMA: the first VPL * WPT * 32 vectors of a tile come through the team's staging buffer.
-        int pending_tile = -1;  // last tile this team asked the copy engine for (chunk-local), if any
-        // asks for the words of chunk-local tile `tile` (vectors off0 .. off1) into buffer tile % R
+        // The first VS * WPT * 32 vectors of a tile come through the team's staging buffer.
+        const uint32_t stage        = w_base + s_own * kStageBytes;
+        int            pending_tile = -1;  // last tile this team asked the copy engine for (chunk-local), if any
+        // asks for the words of chunk-local tile `tile` (vectors off0 .. off1) into the team's buffer
         auto fetch_words = [&](int tile, int off0, int off1) {
             pending_tile = tile;
             if (h == 0 && lane == 0) {
-                const uint32_t bar   = words_full(tile % R);
-                const uint32_t bytes = static_cast<uint32_t>(min(off1 - off0, VPL * WPT * 32)) * 16u;
-                if (bytes > 0 && !(ABL & 4)) {
-                    ptx::mbar_arrive_expect_tx(bar, bytes);
-                    ptx::bulk_copy_g2s(w_base + (tile % R) * kStageBytes, p.words + off0, bytes, bar);
+                const uint32_t bytes = static_cast<uint32_t>(max(min(off1 - off0, VS * WPT * 32), 0)) * 16u;
+                if (bytes > 0) {
+                    ptx::mbar_arrive_expect_tx(words_full(s_own), bytes);
+                    ptx::bulk_copy_g2s(stage, p.words + off0, bytes, words_full(s_own));
                 }
                 else
-                    ptx::mbar_arrive(bar);
-                if (R != D) {
-                    __threadfence_block();
-                    rounds[tile % R] = static_cast<uint32_t>(tile / R);  // the barrier is armed for this round
-                }
+                    ptx::mbar_arrive(words_full(s_own));
             }
         };
-        uint32_t stage = w_base + (s_own % R) * kStageBytes;  // buffer of the tile being decoded
-        auto take_words = [&](int count) {
+        // Staging buffer -> registers.  Every lane reads all of its VPL vectors, whether the tile has
+        // that many or not (the buffer always does; what lies beyond the tile's words is stale and is
+        // never scattered): loads without a branch around them pipeline, 2.8 against 11 cycles each.
+        auto take_words = [&]() {
             uint32_t seen = 0;
 #pragma unroll
-            for (int v = 0; v < VPL; v++)
-                if (lane_vec + v * WPT * 32 < count) {
-                    if (ABL & 4)
-                        r[v] = make_uint4(lane << 17, (lane + 32) << 17, (lane + 64) << 17, (lane + 96) << 17);
-                    else
-                        r[v] = ptx::ld_shared_128(stage + static_cast<uint32_t>(lane_vec + v * WPT * 32) * 16u);
-                    seen ^= r[v].w;
-                }
+            for (int v = 0; v < VS; v++) {
+                r[v] = ptx::ld_shared_128(stage + static_cast<uint32_t>(lane_vec + v * WPT * 32) * 16u);
+                seen ^= r[v].w;
+            }
             // a use of every loaded register: the loads have returned before the buffer is handed
             // back to the copy engine
             asm volatile("" ::"r"(seen) : "memory");
         };
         const uint4* src = p.words + lane_vec;  // always offset by this lane's first vector
         // Offsets are read two tiles ahead (next*: tile l + D, after*: tile l + 2D) so that the words of
-        // tile l + 2D can be requested into L2 while tile l is being decoded; the register loads of
-        // tile l + D, issued after this tile's scatter, then find their lines in L2.
+        // tile l + 2D can be requested into L2 while tile l is being decoded.
         int  after0 = 0, after1 = 0, pf0 = 0, pf1 = 0;
-        int  ring0 = 0, ring1 = 0;  // offsets of tile l + R, read one iteration before they are used
         auto prefetch_tile = [&](int off0, int off1) {
-            if (PFR > 0 && !kMmaRequests && h == 0 && lane == 0 && off1 > off0)
+            if (!kMmaRequests && h == 0 && lane == 0 && off1 > off0)
                 ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
         };
+        if (!p.weights_early)
+            ptx::grid_dependency_wait();
         if (s_own < num_tiles) {
             const int off0 = __ldg(p.tile_offsets + tile_begin + s_own);
             const int off1 = __ldg(p.tile_offsets + tile_begin + s_own + 1);
             nvec           = off1 - off0;
             src            = p.words + off0 + lane_vec;
-            if (WTMA) {
+            if (WTMA)
                 fetch_words(s_own, off0, off1);
-                // the buffers beyond the first round: tiles s_own + D, s_own + 2 D, ... below R
-#pragma unroll 1
-                for (int t = s_own + D; t < R && t < num_tiles; t += D)
-                    fetch_words(t, __ldg(p.tile_offsets + tile_begin + t), __ldg(p.tile_offsets + tile_begin + t + 1));
-            }
-            else
-                load_words(src, nvec);
+            load_words(src, nvec, FromVectorVS{});
             if (s_own + D < num_tiles) {
                 next0 = __ldg(p.tile_offsets + tile_begin + s_own + D);
                 next1 = __ldg(p.tile_offsets + tile_begin + s_own + D + 1);
@@ -434,82 +416,33 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 after1 = __ldg(p.tile_offsets + tile_begin + s_own + 2 * D + 1);
                 prefetch_tile(after0, after1);
             }
-#pragma unroll 1
-            for (int k = 3; k <= PFR; k++)
-                if (s_own + k * D < num_tiles)
-                    prefetch_tile(__ldg(p.tile_offsets + tile_begin + s_own + k * D),
-                                  __ldg(p.tile_offsets + tile_begin + s_own + k * D + 1));
-        }
-        if (WTMA && R != D && s_own + R < num_tiles) {
-            ring0 = __ldg(p.tile_offsets + tile_begin + s_own + R);
-            ring1 = __ldg(p.tile_offsets + tile_begin + s_own + R + 1);
         }
         ptx::grid_dependency_wait();
-        if (BBUF == 2 && s_own < num_tiles)
-            stage_b(j, 0);
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        if (s_own == 0 && h == 0)
-            SPMM_TRACE(1);  // first loads issued
         int use = 0;  // tiles this team has decoded
 #pragma unroll 1
         for (int l = s_own; l < num_tiles; l += D, ++use) {
-            const bool has_next = l + D < num_tiles;
-            const bool fine     = (s_own == 0 && h == 0 && use == 8);
-            (void)fine;
-            const int  lap      = l / S;  // how often this slot has been filled before
-            SPMM_FINE(fine, 0);
-            SPMM_FINE(s_own == 0 && h == 0 && use == 9, 10);
+            const bool     has_next = l + D < num_tiles;
+            const int      lap      = l / S;  // how often this slot has been filled before
+            uint8_t* const a_tile   = smem_generic + slot * kATileBytes;
             if (use > 0)
-                prefetch_tile(pf0, pf1);  // tile l + PFR * D; its offsets were requested one iteration ago
+                prefetch_tile(pf0, pf1);  // tile l + kPrefetchRounds * D; its offsets were read one iteration ago
             if (WTMA) {
-                // this tile's words: staging buffer -> registers, then the buffer takes the next tile
-                stage = w_base + (l % R) * kStageBytes;
-                bool armed = true;
-                if (R != D && l >= R) {
-                    // wait until the buffer has been handed back for this round (it nearly always has)
-                    const uint32_t want  = static_cast<uint32_t>(l / R);
-                    uint64_t       start = 0;
-#pragma unroll 1
-                    for (uint32_t polls = 0; rounds[l % R] < want; polls++) {
-                        if (*abort_word != 0) {
-                            armed = false;
-                            break;
-                        }
-                        if ((polls & 1023u) == 1023u) {
-                            const uint64_t now = ptx::global_timer_ns();
-                            if (start == 0)
-                                start = now;
-                            else if (now - start > ptx::kWaitLimitNs) {
-                                *abort_word = 1;
-                                armed       = false;
-                                break;
-                            }
-                        }
-                    }
-                }
-                if (!armed || !ptx::mbar_wait_bounded(words_full(l % R), (l / R) & 1, abort_word)) {
+                // this tile's words: staging buffer -> registers, then the buffer takes the team's next tile
+                if (!ptx::mbar_wait_bounded(words_full(s_own), use & 1, abort_word)) {
                     if (WPT > 1)
                         asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
                     break;
                 }
-                if (pending_tile == l)
-                    pending_tile = -1;
-                SPMM_FINE(fine, 8);
-                take_words(nvec);
+                pending_tile = -1;
+                take_words();
                 // The copy engine's next write into the staging buffer must not overtake these reads:
                 // they are generic-proxy accesses that may still be queued in the load/store unit when
                 // the bulk copy is issued, so each reader fences before the team barrier (without the
                 // fence two-warp teams gave wrong results on the GPU).
                 ptx::fence_proxy_async_smem();
                 team_sync();
-                // the emptied buffer takes tile l + R (this team's own next tile when R == D)
-                if (l + R < num_tiles) {
-                    if (R == D)
-                        fetch_words(l + R, next0, next1);
-                    else
-                        fetch_words(l + R, ring0, ring1);
-                }
-                SPMM_FINE(fine, 9);
+                if (has_next)
+                    fetch_words(l + D, next0, next1);
             }
             if (lap > 0) {
                 if (!ptx::mbar_wait_bounded(tile_free(slot), (lap - 1) & 1, abort_word)) {
@@ -518,43 +451,24 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
                     break;
                 }
-                SPMM_FINE(fine, 7);
-                if (!(ABL & 1))
-                    zero_a();
+#pragma unroll
+                for (int i = h; i < kATileBytes / (32 * 16); i += WPT)
+                    ptx::st_shared_zero_128(a_base + slot * kATileBytes + lane * 16u + i * 512u);
                 team_sync();  // the whole buffer is clear before anyone scatters into it
             }
-            SPMM_FINE(fine, 1);
-            // The B buffer of the other parity was last read by the tile whose completion was just observed.
-            int j_next = j + D;
-            while (j_next >= tiles_k)
-                j_next -= tiles_k;
-            // With a single B buffer per slot, this tile's own slice is fetched now instead.
-            if (BBUF == 2 ? has_next : true)
-                stage_b(BBUF == 2 ? j_next : j, (use + 1) & 1);
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            SPMM_FINE(fine, 2);
-            if (!(ABL & 2)) {
-#pragma unroll
-                for (int v = 0; v < VPL; v++)
-                    if (lane_vec + v * WPT * 32 < nvec)
-                        ptx::scatter_words(a_tile, r[v]);
-            }
-            // Tiles denser than the register budget (VPL * WPT * 32 vectors): the rest follows in further
+            stage_b(j);  // the slot's B buffer is free as well: this tile's slice (BM == 0, 1)
+            scatter_batch(a_tile, nvec);
+            // Tiles denser than the register budget (kBatch vectors): the rest follows in further
             // register batches; the tile was requested into L2 two rounds ago, so these loads are short.
 #pragma unroll 1
-            for (int done = VPL * WPT * 32; done < nvec; done += VPL * WPT * 32) {
-                load_words(src + done, nvec - done);
-#pragma unroll
-                for (int v = 0; v < VPL; v++)
-                    if (lane_vec + v * WPT * 32 < nvec - done)
-                        ptx::scatter_words(a_tile, r[v]);
+            for (int done = kBatch; done < nvec; done += kBatch) {
+                load_words(src + done, nvec - done, FromVector0{});
+                scatter_batch(a_tile, nvec - done);
             }
-            SPMM_FINE(fine, 3);
             if (has_next) {
                 nvec = next1 - next0;
                 src  = p.words + next0 + lane_vec;
-                if (!WTMA)
-                    load_words(src, nvec);
+                load_words(src, nvec, FromVectorVS{});  // the next tile's directly loaded vectors: in flight from here
                 next0 = after0;
                 next1 = after1;
                 if (l + 3 * D < num_tiles) {
@@ -562,37 +476,28 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     after1 = __ldg(p.tile_offsets + tile_begin + l + 3 * D + 1);
                 }
             }
-            if (WTMA && R != D && l + D + R < num_tiles) {
-                ring0 = __ldg(p.tile_offsets + tile_begin + l + D + R);
-                ring1 = __ldg(p.tile_offsets + tile_begin + l + D + R + 1);
-            }
             pf0 = pf1 = 0;
-            if (l + (PFR + 1) * D < num_tiles) {
-                pf0 = __ldg(p.tile_offsets + tile_begin + l + (PFR + 1) * D);
-                pf1 = __ldg(p.tile_offsets + tile_begin + l + (PFR + 1) * D + 1);
+            if (l + (kPrefetchRounds + 1) * D < num_tiles) {
+                pf0 = __ldg(p.tile_offsets + tile_begin + l + (kPrefetchRounds + 1) * D);
+                pf1 = __ldg(p.tile_offsets + tile_begin + l + (kPrefetchRounds + 1) * D + 1);
             }
-            SPMM_FINE(fine, 4);
-            if (BBUF == 2)
-                asm volatile("cp.async.wait_group 1;" ::: "memory");  // this tile's B slice has landed
-            else
-                asm volatile("cp.async.wait_group 0;" ::: "memory");
-            SPMM_FINE(fine, 5);
+            if (BM == 0)
+                ptx::cp_async_wait_all();  // this tile's B slice has landed
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0)
                 ptx::mbar_arrive(tile_full(slot));
-            SPMM_FINE(fine, 6);
-            j = j_next;
+            j += D;
+            while (j >= tiles_k)
+                j -= tiles_k;
             slot += D;
             if (slot >= S)
                 slot -= S;
-            a_tile = a_base + slot * kATileBytes;
         }
-        ptx::cp_async_wait_all();
+        if (BM == 0)
+            ptx::cp_async_wait_all();
         if (WTMA && pending_tile >= 0)  // only on the way out of an abandoned block
-            ptx::mbar_wait_quiet(words_full(pending_tile % R), (pending_tile / R) & 1, 1000000ull);
-        if (s_own == 0 && h == 0)
-            SPMM_TRACE(6);
+            ptx::mbar_wait_quiet(words_full(s_own), (pending_tile / D) & 1, 1000000ull);
     }
     else if (warp >= kFirstMmaWarp) {
         // ------------------------------------------------------------ MMA issue
@@ -622,7 +527,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     ptx::tma_load_2d(dst + a * BT::kAtomBytes, &p.b_map, static_cast<int>(blockIdx.y) * N + a * BT::kAtomCols,
                                      j * kTileCols, bar);
             };
-            // kMmaRequests: this lane also asks for the words of its tiles PFR laps ahead to be brought into L2
+            // kMmaRequests: this lane also asks for the words of its tiles two laps ahead to be brought into L2
             auto request_words = [&](int off0, int off1) {
                 if (off1 > off0)
                     ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
@@ -632,9 +537,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 for (int l = q; l < S && l < num_tiles; l += Q)
                     load_b(l);
             }
-            if (kMmaRequests && PFR > 0) {
+            if (kMmaRequests) {
 #pragma unroll 1
-                for (int l = q + S; l < PFR * S && l < num_tiles; l += Q)
+                for (int l = q + S; l < kPrefetchRounds * S && l < num_tiles; l += Q)
                     request_words(__ldg(p.tile_offsets + tile_begin + l), __ldg(p.tile_offsets + tile_begin + l + 1));
             }
             bool ok  = true;
@@ -652,10 +557,10 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 for (int l = first; l < l0 + len && ok; l += Q) {
                     const int      s      = l % S;
                     const uint32_t parity = (l / S) & 1;
-                    int            ahead0 = 0, ahead1 = 0;  // offsets of tile l + PFR * S, read while waiting
-                    if (kMmaRequests && PFR > 0 && l + PFR * S < num_tiles) {
-                        ahead0 = __ldg(p.tile_offsets + tile_begin + l + PFR * S);
-                        ahead1 = __ldg(p.tile_offsets + tile_begin + l + PFR * S + 1);
+                    int            ahead0 = 0, ahead1 = 0;  // offsets of tile l + kPrefetchRounds * S, read while waiting
+                    if (kMmaRequests && l + kPrefetchRounds * S < num_tiles) {
+                        ahead0 = __ldg(p.tile_offsets + tile_begin + l + kPrefetchRounds * S);
+                        ahead1 = __ldg(p.tile_offsets + tile_begin + l + kPrefetchRounds * S + 1);
                     }
                     ok = ptx::mbar_wait_bounded(tile_full(s), parity, abort_word);
                     if (!ok)
@@ -664,7 +569,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(s * (kATileBytes >> 4));
                     const uint64_t b_desc = b_desc0 + static_cast<uint64_t>(((BBUF == 2 ? parity : 0) * S + s) * (BT::kBytes >> 4));
 #pragma unroll
-                    for (int k = 0; k < ((ABL & 8) ? 0 : kTileCols / 16); k++) {
+                    for (int k = 0; k < kTileCols / 16; k++) {
                         // A: 16 k values = 32 bytes along the swizzled row; B: 16 k rows = two 8-row groups.
                         ptx::umma_f16_ss(d_tmem,
                                          a_desc + static_cast<uint64_t>((k * 32) >> 4),
@@ -803,7 +708,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 __syncwarp();
                 unsigned int  arrived = 0;
                 unsigned int* counter =
-                    &g_row_arrivals[(blockIdx.y * (p.m / kTileRows) + row_tile) * kEpilogueWarps + warp];
+                    &g_row_arrivals[p.counter_set][(blockIdx.y * (p.m / kTileRows) + row_tile) * kEpilogueWarps + warp];
                 if (lane == 0)
                     arrived = atomicAdd(counter, 1u);
                 arrived = __shfl_sync(0xffffffffu, arrived, 0);
@@ -853,11 +758,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     }
 
     // ---------------------------------------------------------------- exit
-    if (warp == kFirstMmaWarp) SPMM_TRACE(7);   // MMA lane done issuing
-    if (warp == 0) SPMM_TRACE(8);          // epilogue warp 0 done
     ptx::tc_fence_before_sync();
     __syncthreads();
-    if (warp == 0) SPMM_TRACE(9);
     if (threadIdx.x == 0 && *abort_word != 0)
         atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
     if (warp == kFirstMmaWarp) {

@@ -59,6 +59,8 @@ struct StructuredParams {
     int          blocks_k = 0;  // K / 128
     int          m        = 0;
     int          ld       = 0;
+    int          counter_set   = 0;  // which set of arrival counters this launch uses
+    int          weights_early = 0;  // as DecodeParams::weights_early
     Schedule     sched;
 };
 
@@ -131,8 +133,9 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t tmem_e    = tmem_base + 2 * NB;
-    // Programmatic dependent launch, as in the decode kernel: the packed weights are requested at
-    // once, B, C, the workspace and the arrival counters only after the predecessor grid has finished.
+    // Programmatic dependent launch, as in the decode kernel: B, C, the workspace and the arrival counters
+    // are touched only after the predecessor grid has finished; the packed weights are requested at
+    // once if p.weights_early says they were complete before the predecessor started.
     ptx::grid_launch_dependents();
 
     if (warp == kFirstMmaWarp + 1) {
@@ -140,6 +143,8 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
         // Lane 0 copies the values, lane 1 the metadata, in one instruction: issuing a bulk copy
         // costs the issuing thread a few hundred cycles, and one thread issuing both copies of every
         // block would be close to the time a block may take at full memory bandwidth.
+        if (!p.weights_early)
+            ptx::grid_dependency_wait();
         if (lane < 2) {
             int            issued = 0;
             const uint32_t bytes  = lane == 0 ? kBlockValueBytes : kBlockMetaBytes;
@@ -336,7 +341,7 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
                 __threadfence();
                 __syncwarp();
                 unsigned int  arrived = 0;
-                unsigned int* counter = &g_row_arrivals[row_tile * kEpilogueWarps + warp];
+                unsigned int* counter = &g_row_arrivals[p.counter_set][row_tile * kEpilogueWarps + warp];
                 if (lane == 0)
                     arrived = atomicAdd(counter, 1u);
                 arrived = __shfl_sync(0xffffffffu, arrived, 0);

@@ -14,6 +14,14 @@ import numpy as np
 
 from . import build as _build
 
+class HostIoItem(ctypes.Structure):
+    """spmm_b200_host_io_item of include/spmm_b200.h."""
+    _fields_ = [("Compressed_A", ctypes.c_void_p), ("TileOffsets", ctypes.c_void_p), ("B_host", ctypes.c_void_p),
+                ("C_host", ctypes.c_void_p), ("B_dev", ctypes.c_void_p), ("C_dev", ctypes.c_void_p),
+                ("M", ctypes.c_int), ("N", ctypes.c_int), ("K", ctypes.c_int),
+                ("Reduction_Workspace", ctypes.c_void_p), ("Split_K", ctypes.c_int)]
+
+
 _u16p = ctypes.POINTER(ctypes.c_uint16)
 _u32p = ctypes.POINTER(ctypes.c_uint32)
 _i32p = ctypes.POINTER(ctypes.c_int)
@@ -43,6 +51,8 @@ def _load():
     lib.spmm_b200_spmm_splitk.restype = ctypes.c_int
     lib.spmm_b200_spmm_splitk_host_io.argtypes = [ctypes.c_void_p] * 7 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
     lib.spmm_b200_spmm_splitk_host_io.restype = ctypes.c_int
+    lib.spmm_b200_spmm_splitk_host_io_batch.argtypes = [ctypes.c_void_p, ctypes.c_int, ctypes.POINTER(HostIoItem)]
+    lib.spmm_b200_spmm_splitk_host_io_batch.restype = ctypes.c_int
     lib.spmm_b200_spmm_own_scratch.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3
     lib.spmm_b200_spmm_own_scratch.restype = ctypes.c_int
     lib.spmm_b200_spmm_splitk_token_major.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
@@ -54,8 +64,14 @@ def _load():
                                                  ctypes.c_int, ctypes.c_int, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_uint32,
                                                  ctypes.c_uint]
     lib.spmm_b200_allreduce_partials.restype = ctypes.c_int
+    lib.spmm_b200_allreduce_partials_replayable.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                                            ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int,
+                                                            ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_uint]
+    lib.spmm_b200_allreduce_partials_replayable.restype = ctypes.c_int
     lib.spmm_b200_allreduce_status.argtypes = [ctypes.c_int]
     lib.spmm_b200_allreduce_status.restype = ctypes.c_int
+    lib.spmm_b200_set_weights_constant.argtypes = [ctypes.c_int]
+    lib.spmm_b200_set_weights_constant.restype = ctypes.c_int
     lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
     for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):
@@ -68,6 +84,8 @@ def _load():
     lib.spmm_b200_selftest_wait_timeout.restype = ctypes.c_int
     lib.spmm_b200_synth_fp16.argtypes = [_u16p, ctypes.c_long, ctypes.c_uint64, ctypes.c_double, ctypes.c_double]
     lib.spmm_b200_synth_fp16.restype = None
+    lib.spmm_b200_synth_fp16_block.argtypes = [_u16p] + [ctypes.c_long] * 5 + [ctypes.c_uint64, ctypes.c_double, ctypes.c_double]
+    lib.spmm_b200_synth_fp16_block.restype = None
     lib.spmm_b200_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_long, _i32p, _i32p, _i32p]
     lib.spmm_b200_plan.restype = ctypes.c_int
     lib.GenSparseMatrixBinFile.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p,
@@ -162,6 +180,32 @@ def SpMM_SplitK_API_host_io(stream, Compressed_A, TileOffsets, B_host, C_host, B
                                              _dev_ptr(Reduction_Workspace), Split_K)
 
 
+def host_io_items(layers):
+    """Packs dicts with the keys of spmm_b200_host_io_item (tensors or raw pointers) into a ctypes array for
+    SpMM_SplitK_API_host_io_batch; build it once and reuse it."""
+    arr = (HostIoItem * len(layers))()
+    for item, L in zip(arr, layers):
+        for key in ("Compressed_A", "TileOffsets", "B_dev", "C_dev", "Reduction_Workspace"):
+            setattr(item, key, _dev_ptr(L[key]).value if L[key] is not None else None)
+        for key in ("B_host", "C_host"):
+            if L[key].is_cuda:
+                raise ValueError("%s must be a CPU tensor" % key)
+            setattr(item, key, L[key].data_ptr())
+        item.M, item.N, item.K, item.Split_K = L["M"], L["N"], L["K"], L["Split_K"]
+    return arr
+
+
+def SpMM_SplitK_API_host_io_batch(stream, items):
+    """Several host-buffer products in one call (e.g. the layers of a decoder block): activations are copied in on a
+    copy stream ahead of the products, each result is copied out while the next product runs.  `items`: what
+    host_io_items returned.  After the call `stream` waits for the last copy.  Returns a cudaError_t as an int."""
+    import torch
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    handle = stream if isinstance(stream, int) else stream.cuda_stream
+    return LIB.spmm_b200_spmm_splitk_host_io_batch(ctypes.c_void_p(handle), len(items), items)
+
+
 def SpMM_SplitK_API_token_major(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global, K_Global,
                                 Reduction_Workspace, Split_K):
     """The upstream eleven-argument form the FasterTransformer glue calls (third_party/ft.patch:2822-2846):
@@ -185,6 +229,12 @@ def spmm_own_scratch(stream, Compressed_A, TileOffsets, B, C, M_Global, N_Global
     handle = stream if isinstance(stream, int) else stream.cuda_stream
     return LIB.spmm_b200_spmm_own_scratch(ctypes.c_void_p(handle), _dev_ptr(Compressed_A), _dev_ptr(TileOffsets),
                                           _dev_ptr(B), _dev_ptr(C), M_Global, N_Global, K_Global)
+
+
+def set_weights_constant(constant=True):
+    """Whether weights may be fetched before the stream predecessor has completed (see include/spmm_b200.h:
+    the caller guarantees they are not produced by the kernel just ahead).  Returns the previous setting."""
+    return bool(LIB.spmm_b200_set_weights_constant(1 if constant else 0))
 
 
 def workspace_bytes(M_Global, N_Global, Split_K):
@@ -248,6 +298,13 @@ def synth_fp16(shape, seed, sigma, p_zero=0.0):
     """Seeded synthetic fp16 data (uint16 bits): sigma * N(0,1), zeroed with probability p_zero."""
     out = np.empty(shape, np.uint16)
     LIB.spmm_b200_synth_fp16(out.ctypes.data_as(_u16p), out.size, seed, float(sigma), float(p_zero))
+    return out
+
+
+def synth_fp16_block(rows, cols, ld, row0, col0, seed, sigma, p_zero=0.0):
+    """The rows x cols block at (row0, col0) of the matrix synth_fp16((R, ld), seed, ...) would return."""
+    out = np.empty((rows, cols), np.uint16)
+    LIB.spmm_b200_synth_fp16_block(out.ctypes.data_as(_u16p), rows, cols, ld, row0, col0, seed, float(sigma), float(p_zero))
     return out
 
 

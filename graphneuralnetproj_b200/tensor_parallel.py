@@ -66,9 +66,14 @@ class PeerAllReduce:
 
     Holds two symmetric result buffers per rank (the SpMM of call n writes into `next_buffer()`, the
     kernel of call n reads all ranks' copies of it) and one symmetric flag array.  Every rank must
-    construct it and call `reduce` the same number of times.  One process per GPU."""
+    construct it and call `reduce` the same number of times.  One process per GPU.
 
-    def __init__(self, count, device, group=None):
+    `replayable=True` keeps the epoch in device memory so that `reduce` can be captured in a CUDA graph
+    and replayed.  The buffer used by a call is then fixed at capture time (calls alternate between the
+    two as usual), so a graph must either contain an even number of calls of this object or other
+    exchanges among the same ranks between two of them (see include/spmm_b200.h)."""
+
+    def __init__(self, count, device, group=None, replayable=False):
         import ctypes
         import os
 
@@ -95,6 +100,7 @@ class PeerAllReduce:
         self._buffer_ptrs = [ptr_array(*[int(p) for p in h.buffer_ptrs]) for h in handles]
         self._flag_ptrs = ptr_array(*[int(p) for p in flag_handle.buffer_ptrs])
         self.out = torch.empty(count, dtype=torch.float16, device=device)
+        self.state = torch.zeros(2, dtype=torch.int32, device=device) if replayable else None
         self.epoch = 0
         torch.cuda.synchronize(device)
         dist.barrier(group)  # nobody signals before every flag array is zero
@@ -111,9 +117,14 @@ class PeerAllReduce:
         if stream is None:
             stream = torch.cuda.current_stream()
         self.epoch += 1
-        rc = self._api.LIB.spmm_b200_allreduce_partials(ctypes.c_void_p(stream.cuda_stream), self._buffer_ptrs[self.epoch & 1],
-                                                        self._flag_ptrs, self.rank, self.world,
-                                                        ctypes.c_void_p(self.out.data_ptr()), self.count, self.epoch, limit_ms)
+        if self.state is not None:
+            rc = self._api.LIB.spmm_b200_allreduce_partials_replayable(
+                ctypes.c_void_p(stream.cuda_stream), self._buffer_ptrs[self.epoch & 1], self._flag_ptrs, self.rank, self.world,
+                ctypes.c_void_p(self.out.data_ptr()), self.count, ctypes.c_void_p(self.state.data_ptr()), limit_ms)
+        else:
+            rc = self._api.LIB.spmm_b200_allreduce_partials(
+                ctypes.c_void_p(stream.cuda_stream), self._buffer_ptrs[self.epoch & 1], self._flag_ptrs, self.rank, self.world,
+                ctypes.c_void_p(self.out.data_ptr()), self.count, self.epoch, limit_ms)
         if rc != 0:
             raise RuntimeError("spmm_b200_allreduce_partials failed with cudaError %d" % rc)
         return self.out
@@ -123,7 +134,7 @@ class RowParallelSpMM:
     """One rank's part of a row-parallel layer on its GPU: SpMM over its K shard, then the sum over ranks,
     by NCCL (`reduce="nccl"`) or by the library's own peer-memory kernel (`reduce="peer"`)."""
 
-    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, reduce="nccl", group=None):
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, reduce="nccl", group=None, replayable=False):
         import torch
         from . import spmm_api
         self._api = spmm_api
@@ -133,7 +144,7 @@ class RowParallelSpMM:
         dev = words_dev.device
         self.C = torch.zeros((M, N), dtype=torch.float16, device=dev)
         self.workspace = torch.zeros(spmm_api.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
-        self.peer = PeerAllReduce(M * N, dev, group) if reduce == "peer" else None
+        self.peer = PeerAllReduce(M * N, dev, group, replayable=replayable) if reduce == "peer" else None
 
     def forward(self, B_shard_dev, group=None):
         C = self.peer.next_buffer() if self.peer is not None else self.C

@@ -68,6 +68,30 @@ int spmm_b200_spmm_splitk_host_io(void*       stream,
                                   void*       Reduction_Workspace,
                                   int         Split_K);
 
+/* Several spmm_b200_spmm_splitk_host_io products in one call, e.g. the linear layers of a decoder
+ * block: the copies of the activations run on a copy stream of the library ahead of the products,
+ * and every result travels back on a second copy stream while the next product runs on `stream`.
+ * When the call returns everything is queued; `stream` has been made to wait for the last copy, so
+ * synchronising `stream` (or queueing more work on it) is enough to read C_host.  The library keeps
+ * two streams and a few events per device for this (created by the first call on the device, which
+ * should not fall inside a stream capture).  count: 1 .. SPMM_B200_HOST_IO_MAX_ITEMS.  Calls are
+ * serialised by a lock.  Returns the first cudaError_t met, as an int.  The reference's harness
+ * does the same copies with blocking cudaMemcpy calls (kernel_benchmark/spmm_test.cu:118-137,
+ * 565-567). */
+#define SPMM_B200_HOST_IO_MAX_ITEMS 16
+typedef struct spmm_b200_host_io_item {
+    const void* Compressed_A;
+    const int*  TileOffsets;
+    const void* B_host; /* K * N halves, page-locked */
+    void*       C_host; /* M * N halves, page-locked */
+    void*       B_dev;  /* device staging for B */
+    void*       C_dev;  /* device staging for C */
+    int         M, N, K;
+    void*       Reduction_Workspace;
+    int         Split_K;
+} spmm_b200_host_io_item;
+int spmm_b200_spmm_splitk_host_io_batch(void* stream, int count, const spmm_b200_host_io_item* items);
+
 /* The eleven-argument upstream form of SpMM_SplitK_API that the reference's FasterTransformer
  * glue calls (third_party/ft.patch:2822-2846), with token-major layouts: B[N][K], C[N][M]. */
 int spmm_b200_spmm_splitk_token_major(void*       stream,
@@ -124,8 +148,38 @@ int spmm_b200_allreduce_partials(void*              stream,
                                  size_t             count,
                                  uint32_t           epoch,
                                  unsigned           limit_ms);
+/* The same reduction for callers that capture it in a CUDA graph and replay it: the epoch is not an
+ * argument but lives on the device.  state: two 32-bit words of this rank's device memory, zero before
+ * the first call and used by nothing else; every launch reads its epoch from them and its last block
+ * advances it, so every replay carries a new epoch.  All ranks must make the same sequence of calls
+ * on the same state.  The partial buffers are fixed at capture time: between two launches that use
+ * the same partial buffers there must be another exchange among the same ranks (a second set of
+ * buffers used alternately, or another layer's reduction), otherwise a fast rank's next product
+ * could overwrite what a slow peer is still reading. */
+int spmm_b200_allreduce_partials_replayable(void*              stream,
+                                            const void* const* partial_buffers,
+                                            void* const*       flag_arrays,
+                                            int                rank,
+                                            int                world,
+                                            void*              out,
+                                            size_t             count,
+                                            void*              state,
+                                            unsigned           limit_ms);
 /* 0, or 1 if a wait inside spmm_b200_allreduce_partials ran out (synchronises the device). */
 int spmm_b200_allreduce_status(int reset);
+
+/* Tells the library whether the weights of every SpMM (Compressed_A, TileOffsets, and in the
+ * heterogeneous mode A and metadata) are constant while kernels run, as inference weights are.
+ * The kernels are launched so that they may start while the kernel ahead of them in the stream is
+ * still draining (programmatic dependent launch).  By default (0) they read nothing before that
+ * predecessor has completed, so a stream in which the preceding kernel produces the weights
+ * (dequantisation, a copy, a device-side encoder) is safe.  With 1 the weights and offsets are
+ * fetched at once, ahead of the predecessor's completion, which hides the start-up of a launch
+ * behind the end of the previous one; the caller then guarantees that the weights were complete
+ * before the preceding kernel in the stream started (e.g. by one synchronisation after upload).
+ * Process-wide; returns the previous setting.  No counterpart in the reference, whose launches are
+ * fully serialised. */
+int spmm_b200_set_weights_constant(int constant);
 
 /* The reference's workspace contract, build/SpMM_API.cuh:34-38:
  * Split_K * M * N * sizeof(half) bytes. */
@@ -164,6 +218,13 @@ int spmm_b200_selftest_wait_timeout(void* stream, unsigned int limit_ms);
  * probability p_zero.  No counterpart in the reference, whose harness uses
  * rand() (kernel_benchmark/spmm_test_utils.h:108-162). */
 void spmm_b200_synth_fp16(uint16_t* out, long count, uint64_t seed, double sigma, double p_zero);
+
+/* The same stream, for the rows x cols block at (row0, col0) of a virtual row-major matrix with ld
+ * columns (out is rows x cols, contiguous): element (r, c) of the block is element
+ * (row0 + r) * ld + col0 + c of the stream.  Lets a tensor-parallel rank draw only its own shard
+ * of a layer, identical to cutting it out of the whole matrix.  No counterpart in the reference. */
+void spmm_b200_synth_fp16_block(
+    uint16_t* out, long rows, long cols, long ld, long row0, long col0, uint64_t seed, double sigma, double p_zero);
 
 /* The work partition the SpMM kernel would use (for tests of the host logic):
  * fills chunk_begin[0..ctas] and split_rows_above[0..ctas-1], returns the

@@ -61,6 +61,8 @@ def lib():
             f = getattr(L, name)
             f.argtypes = [_u16p, _u16p, _u16p, ctypes.c_int]
             f.restype = None
+        L.oracle_synth_fp16_block.argtypes = [_u16p] + [ctypes.c_long] * 5 + [ctypes.c_uint64, ctypes.c_double, ctypes.c_double]
+        L.oracle_synth_fp16_block.restype = None
         _lib = L
     return _lib
 
@@ -163,6 +165,50 @@ def spmm_f64(A, B):
     C = np.empty((M, N), np.float64)
     lib().oracle_spmm_f64(A.ctypes.data_as(_u16p), B.ctypes.data_as(_u16p), C.ctypes.data_as(_f64p), M, N, K)
     return C
+
+
+def synth_fp16_block(rows, cols, ld, row0, col0, seed, sigma, p_zero=0.0, threads=None):
+    """Seeded synthetic fp16 bits: the rows x cols block at (row0, col0) of a virtual matrix with ld columns
+    (bit-identical to the product library's generator, written independently); row blocks on host threads."""
+    import threading
+    out = np.empty((rows, cols), np.uint16)
+    threads = max(1, min(threads or (os.cpu_count() or 1), 64, rows))
+    bounds = [rows * t // threads for t in range(threads + 1)]
+
+    def work(t):
+        r0, r1 = bounds[t], bounds[t + 1]
+        if r1 > r0:
+            lib().oracle_synth_fp16_block(out[r0:r1].ctypes.data_as(_u16p), r1 - r0, cols, ld, row0 + r0, col0, seed,
+                                          float(sigma), float(p_zero))
+
+    lib()
+    pool = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+    for th in pool:
+        th.start()
+    for th in pool:
+        th.join()
+    return out
+
+
+def spmm_f64_threads(A, B, threads=None):
+    """spmm_f64 over row blocks on several host threads (the C loop releases the interpreter lock)."""
+    import threading
+    A = _as_u16(A)
+    M = A.shape[0]
+    threads = max(1, min(threads or (os.cpu_count() or 1), 32, M))
+    out = np.empty((M, B.shape[1]), np.float64)
+    bounds = [M * t // threads for t in range(threads + 1)]
+
+    def work(t):
+        if bounds[t + 1] > bounds[t]:
+            out[bounds[t]:bounds[t + 1]] = spmm_f64(A[bounds[t]:bounds[t + 1]], B)
+
+    pool = [threading.Thread(target=work, args=(t,)) for t in range(threads)]
+    for th in pool:
+        th.start()
+    for th in pool:
+        th.join()
+    return out
 
 
 def spmm_from_csl(words, offsets, B, M, K):

@@ -442,3 +442,41 @@ void oracle_decompose_v1(const uint16_t* A, uint16_t* A1, uint16_t* A2, int leng
             }
     }
 }
+
+/*
+ * Seeded synthetic inputs for the CPU-side legs of the benchmark (no counterpart in the reference,
+ * whose harness draws from rand(), kernel_benchmark/spmm_test_utils.h:108-162): element i of a
+ * stream is fp16(sigma * gaussian), zeroed with probability p_zero, from three counter-based
+ * splitmix64 uniforms (Box-Muller).  Written here independently so that the CPU legs need nothing
+ * from the product library; tests compare the two generators bit for bit.  Fills the rows x cols
+ * block at (row0, col0) of a virtual row-major matrix with ld columns.
+ */
+static uint64_t synth_mix(uint64_t seed, uint64_t index)
+{
+    uint64_t z = seed + (index + 1) * 0x9e3779b97f4a7c15ull;
+    z          = (z ^ (z >> 30)) * 0xbf58476d1ce4e5b9ull;
+    z          = (z ^ (z >> 27)) * 0x94d049bb133111ebull;
+    return z ^ (z >> 31);
+}
+
+static double synth_unit(uint64_t x)
+{
+    return ((double)(x >> 11) + 0.5) * (1.0 / 9007199254740992.0);
+}
+
+void oracle_synth_fp16_block(uint16_t* out, long rows, long cols, long ld, long row0, long col0, uint64_t seed, double sigma,
+                             double p_zero)
+{
+    for (long r = 0; r < rows; r++)
+        for (long c = 0; c < cols; c++) {
+            const uint64_t base = (uint64_t)((row0 + r) * ld + col0 + c) * 3u;
+            uint16_t       bits = 0;
+            if (!(synth_unit(synth_mix(seed, base + 2)) < p_zero)) {
+                const double u1 = synth_unit(synth_mix(seed, base));
+                const double u2 = synth_unit(synth_mix(seed, base + 1));
+                const double g  = sqrt(-2.0 * log(u1)) * cos(6.283185307179586476925 * u2);
+                bits            = oracle_float_to_half((float)(sigma * g));
+            }
+            out[r * cols + c] = bits;
+        }
+}
