@@ -5,7 +5,8 @@ import subprocess
 _HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(_HERE, "csrc")
 LIB_PATH = os.path.join(_HERE, "libSpMM_API.so")
-SOURCES = ["spmm_api.cu", "encode_tiled_csl.cu", "encode_structured.cu", "pack_a1_tcgen05.cu", "allreduce_peer.cu", "host_utils.cu"]
+SOURCES = ["spmm_api.cu", "encode_tiled_csl.cu", "encode_structured.cu", "pack_a1_tcgen05.cu", "allreduce_peer.cu", "host_utils.cu",
+           "validate.cu", "model_files.cu"]
 NVCC_FLAGS = [
     "-std=c++17", "-O3", "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo",
     "-Xcompiler", "-fPIC", "-shared",

@@ -22,13 +22,22 @@ namespace {
 // held per lane (WPT * VPL * 32 vectors = 7168 bytes of words in flight per team).
 // Up to 64 columns the kernel is bound by decoding; 128 and 256 columns serve prefill sizes, where a
 // decoded tile feeds four 128 x N x 16 MMAs of 64-128 cycles each and fewer, wider slots are enough.
+#ifndef SPMM_B200_D16
+#define SPMM_B200_D16 8
+#endif
+#ifndef SPMM_B200_S16
+#define SPMM_B200_S16 8
+#endif
+#ifndef SPMM_B200_BM16
+#define SPMM_B200_BM16 2
+#endif
 template<int N>
 struct DecodeConfig {
-    static constexpr int D    = N <= 64 ? 8 : 4;   // decoder teams
+    static constexpr int D    = N == 16 ? (SPMM_B200_D16) : (N <= 64 ? 8 : 4);   // decoder teams
     static constexpr int WPT  = N <= 64 ? 1 : 2;   // warps per team
     static constexpr int Q    = N <= 64 ? 4 : (N == 128 ? 2 : 1);  // MMA-issuing warps (2 * Q * N TMEM columns)
     static constexpr int VPL  = 14 / WPT;
-    static constexpr int S    = N <= 64 ? 8 : (N == 128 ? 6 : 4);  // ring slots
+    static constexpr int S    = N == 16 ? (SPMM_B200_S16) : (N <= 64 ? 8 : (N == 128 ? 6 : 4));  // ring slots
     // vectors per lane that are staged through shared memory by bulk copy (the rest are loaded straight
     // into registers); none at N = 64, where staging buffers do not fit beside eight 16 KB A buffers
     // and eight 8 KB B slices
@@ -39,7 +48,7 @@ struct DecodeConfig {
     // B slices (row-major layout): tiled TMA loads, issued by the MMA warps a lap ahead into a second
     // B buffer where that fits in shared memory (N <= 16), else by the tile's decoder
     // (N = 8 keeps the 16-byte copies: its staged rows are twice as wide as the rows of B)
-    static constexpr int BM   = N == 8 ? 0 : (N == 16 ? 2 : 1);
+    static constexpr int BM   = N == 8 ? 0 : (N == 16 ? (SPMM_B200_BM16) : 1);
 };
 
 struct DeviceInfo {

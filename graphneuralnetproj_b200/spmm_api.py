@@ -86,6 +86,17 @@ def _load():
     lib.spmm_b200_synth_fp16.restype = None
     lib.spmm_b200_synth_fp16_block.argtypes = [_u16p] + [ctypes.c_long] * 5 + [ctypes.c_uint64, ctypes.c_double, ctypes.c_double]
     lib.spmm_b200_synth_fp16_block.restype = None
+    lib.spmm_b200_validate_tiled_csl.argtypes = [ctypes.c_void_p, ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p,
+                                                 ctypes.c_int, ctypes.c_int]
+    lib.spmm_b200_validate_tiled_csl.restype = ctypes.c_int
+    lib.spmm_b200_validate_tiled_csl_host.argtypes = [_u32p, ctypes.c_size_t, _i32p, ctypes.c_int, ctypes.c_int]
+    lib.spmm_b200_validate_tiled_csl_host.restype = ctypes.c_int
+    lib.spmm_b200_shard_shapes.argtypes = [ctypes.c_int, ctypes.c_int, _i32p, _i32p]
+    lib.spmm_b200_shard_shapes.restype = ctypes.c_int
+    lib.spmm_b200_suggest_split_k.argtypes = [ctypes.c_int, ctypes.c_int]
+    lib.spmm_b200_suggest_split_k.restype = ctypes.c_int
+    lib.spmm_b200_write_rank_lists.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, _i32p, _i32p]
+    lib.spmm_b200_write_rank_lists.restype = ctypes.c_int
     lib.spmm_b200_plan.argtypes = [ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_long, _i32p, _i32p, _i32p]
     lib.spmm_b200_plan.restype = ctypes.c_int
     lib.GenSparseMatrixBinFile.argtypes = [ctypes.c_char_p, ctypes.c_int, ctypes.c_int, ctypes.c_char_p, ctypes.c_char_p,
@@ -281,6 +292,50 @@ def InitSparseMatrixA1_tcgen05(A1_h, M, K):
 def GenSparseMatrixBinFile(dense_path, M, K, nz_path, offsets_path, sizes_path):
     """File front end used by the weight-conversion tools (csrc/SpMM_API.cu:1565-1620)."""
     LIB.GenSparseMatrixBinFile(dense_path.encode(), M, K, nz_path.encode(), offsets_path.encode(), sizes_path.encode())
+
+
+CSL_FINDINGS = {1: "first offset not zero", 2: "offsets decrease", 4: "last offset not repeated",
+                8: "offsets do not cover the words given", 16: "a position lies outside the tile", 32: "bad argument"}
+
+
+def validate_tiled_csl(words, offsets, M, K, stream=None):
+    """0 if the tiled-CSL stream is well formed, else a mask of CSL_FINDINGS keys.  numpy arrays are checked on the
+    host, CUDA tensors by a kernel on `stream` (which is synchronised)."""
+    if isinstance(words, np.ndarray):
+        words = np.ascontiguousarray(words, dtype=np.uint32)
+        offsets = np.ascontiguousarray(offsets, dtype=np.int32)
+        if offsets.size != (M // TILE_M) * (K // TILE_K) + 2:
+            return 32
+        return int(LIB.spmm_b200_validate_tiled_csl_host(words.ctypes.data_as(_u32p), words.size,
+                                                          offsets.ctypes.data_as(_i32p), M, K))
+    import torch
+    if offsets.numel() != (M // TILE_M) * (K // TILE_K) + 2:
+        return 32
+    if stream is None:
+        stream = torch.cuda.current_stream()
+    return int(LIB.spmm_b200_validate_tiled_csl(ctypes.c_void_p(stream.cuda_stream), _dev_ptr(words), words.numel(),
+                                                _dev_ptr(offsets), M, K))
+
+
+def shard_shapes(hidden, world):
+    """(M[4], K[4]) of one rank's shards of query_key_value, attention.dense, dense_h_to_4h, dense_4h_to_h."""
+    M, K = (ctypes.c_int * 4)(), (ctypes.c_int * 4)()
+    if LIB.spmm_b200_shard_shapes(hidden, world, M, K) != 0:
+        raise ValueError("hidden size %d cannot be split %d ways into whole tiles" % (hidden, world))
+    return list(M), list(K)
+
+
+def suggest_split_k(M, K):
+    """A Split_K whose workspace (Split_K * M * N halves) holds the partial tiles of the partition over all SMs."""
+    return int(LIB.spmm_b200_suggest_split_k(M, K))
+
+
+def write_rank_lists(model_dir, rank, num_layers, M, K):
+    """Writes NNZ_List/NumOffsets_List/SplitK_List.<rank>.bin from the .OutputSizes.bin files in model_dir."""
+    n = LIB.spmm_b200_write_rank_lists(model_dir.encode(), rank, num_layers, (ctypes.c_int * 4)(*M), (ctypes.c_int * 4)(*K))
+    if n < 0:
+        raise OSError("could not read the sizes files or write the list files in " + model_dir)
+    return n
 
 
 def device_status(reset=False):

@@ -226,6 +226,42 @@ void spmm_b200_synth_fp16(uint16_t* out, long count, uint64_t seed, double sigma
 void spmm_b200_synth_fp16_block(
     uint16_t* out, long rows, long cols, long ld, long row0, long col0, uint64_t seed, double sigma, double p_zero);
 
+/* Checks a tiled-CSL stream before it is given to the SpMM, whose kernels trust it (a word's position
+ * addresses the tile buffer in shared memory, consecutive offsets size the copies): TileOffsets starts
+ * at 0, never decreases, repeats its last entry ((M/128)*(K/64) + 2 entries), covers exactly n_words
+ * words, and every position is below 128*64.  The reference asserts these inside its encoder only
+ * (csrc/SpMM_API.cu:354-356, 380, 431); files can be truncated or corrupt.  Reads nothing beyond
+ * n_words words and the offsets; never traps.  Returns 0 if well formed, a mask of the findings
+ * below, or minus a cudaError_t.  The device version runs on `stream` and synchronises it. */
+#define SPMM_B200_CSL_FIRST_OFFSET_NOT_ZERO 1
+#define SPMM_B200_CSL_OFFSETS_DECREASE 2
+#define SPMM_B200_CSL_TAIL_NOT_REPEATED 4
+#define SPMM_B200_CSL_WORD_COUNT_MISMATCH 8
+#define SPMM_B200_CSL_POSITION_OUT_OF_TILE 16
+#define SPMM_B200_CSL_BAD_ARGUMENT 32
+int spmm_b200_validate_tiled_csl(void* stream, const void* Compressed_A, size_t n_words, const int* TileOffsets, int M, int K);
+int spmm_b200_validate_tiled_csl_host(const uint32_t* Compressed_A, size_t n_words, const int* TileOffsets, int M, int K);
+
+/* Tensor-parallel shard shapes of the four linear layers of a decoder block (query_key_value,
+ * attention.dense, dense_h_to_4h, dense_4h_to_h) on one of `world` ranks, as the reference's conversion
+ * tool splits them (end2end_inference/ft_tools/huggingface_opt_convert_Phase2.py:134-135):
+ * M = {3h/g, h, 4h/g, h}, K = {h, h/g, h, 4h/g}.  Returns 0, or -1 if a shard is not a whole number
+ * of 128 x 64 tiles. */
+int spmm_b200_shard_shapes(int hidden, int world, int* M, int* K);
+
+/* A Split_K for spmm_b200_spmm_splitk's workspace contract (Split_K * M * N halves) that is large
+ * enough for the partition over all SMs of an M x K layer; takes the place of the reference's
+ * hand-tuned table (huggingface_opt_convert_Phase2.py:20, kernel_benchmark/benchmark.sh:13-15).
+ * 0 for shapes the format cannot describe. */
+int spmm_b200_suggest_split_k(int M, int K);
+
+/* Writes NNZ_List.<rank>.bin, NumOffsets_List.<rank>.bin and SplitK_List.<rank>.bin into model_dir
+ * (huggingface_opt_convert_Phase2.py:183-195; read by third_party/ft.patch:2352-2401): one int32 per
+ * (layer, matrix), matrices in the order above, from the .OutputSizes.bin that GenSparseMatrixBinFile
+ * wrote for model.layers.<layer>.<matrix>.weight.<rank>; matrices without one (left dense) get 0.
+ * M, K: the rank's four shard shapes.  Returns the number of sparse matrices found, -1 on an I/O error. */
+int spmm_b200_write_rank_lists(const char* model_dir, int rank, int num_layers, const int* M, const int* K);
+
 /* The work partition the SpMM kernel would use (for tests of the host logic):
  * fills chunk_begin[0..ctas] and split_rows_above[0..ctas-1], returns the
  * number of thread blocks; *slots_used gets the number of workspace slots. */

@@ -29,8 +29,11 @@ _f64p = ctypes.POINTER(ctypes.c_double)
 
 
 def build():
-    """Compile the C restatement and, when the reference tree is present, the reference library."""
-    subprocess.check_call(["make", "-s", "-C", _HERE])
+    """Compile the C restatement and, when the reference tree is present (REFERENCE_ROOT in the environment, or a
+    directory named `reference` beside this repository), the reference libraries."""
+    beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
+    root = os.environ.get("REFERENCE_ROOT") or (beside if os.path.isfile(os.path.join(beside, "csrc", "SpMM_API.cu")) else "")
+    subprocess.check_call(["make", "-s", "-C", _HERE] + (["REFERENCE_ROOT=" + root] if root else []))
 
 
 _lib = None
@@ -69,6 +72,28 @@ def lib():
 
 def have_ref():
     return os.path.exists(_REF_SO)
+
+
+_REF_DECOMPOSE_SO = os.path.join(_HERE, "_ref", "libdecompose_ref.so")
+
+
+def have_ref_decompose():
+    return os.path.exists(_REF_DECOMPOSE_SO)
+
+
+def ref_decompose(A, v1=False):
+    """decompose / decompose_v1 of the compiled reference header (kernel_benchmark/spmm_decompose.h:12,53).
+    Prints the reference's statistics lines to stdout, as the reference does."""
+    R = ctypes.CDLL(_REF_DECOMPOSE_SO)
+    fn = getattr(R, "_Z12decompose_v1P6__halfS0_S0_i" if v1 else "_Z9decomposeP6__halfS0_S0_i")
+    fn.argtypes = [_u16p, _u16p, _u16p, ctypes.c_int]
+    fn.restype = None
+    A = _as_u16(A)
+    flat = np.ascontiguousarray(A.reshape(-1))
+    A1 = np.empty_like(flat)
+    A2 = np.empty_like(flat)
+    fn(flat.ctypes.data_as(_u16p), A1.ctypes.data_as(_u16p), A2.ctypes.data_as(_u16p), flat.size)
+    return A1.reshape(A.shape), A2.reshape(A.shape)
 
 
 # Itanium-mangled names of the reference's C++ entry points (build/SpMM_API.cuh:54-96).

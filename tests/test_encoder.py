@@ -88,6 +88,24 @@ def test_decompose_matches_oracle(sp, oracle):
         assert np.array_equal(a1, b1) and np.array_equal(a2, b2)
 
 
+def test_decompose_matches_compiled_reference(sp, oracle, capfd):
+    """decompose / decompose_v1 against the reference's own header (kernel_benchmark/spmm_decompose.h:12-142),
+    compiled as it lies into oracle/_ref: groups with 0..4 nonzeros, -0, NaN, subnormals."""
+    import pytest
+    if not oracle.have_ref_decompose():
+        pytest.skip("compiled reference header not present")
+    A = sp.synth_fp16((256, 192), 4321, 0.02, 0.55)
+    A[0, :8] = [0x8000, 0x0001, 0x7E00, 0x3C00, 0x0000, 0x8000, 0x8000, 0xFC00]  # -0, subnormal, NaN, 1, 0, -0, -0, -inf
+    A[1, :4] = 0x3C00                                                           # a full group
+    for v1 in (False, True):
+        a1, a2 = sp.decompose(A, v1=v1)
+        r1, r2 = oracle.ref_decompose(A, v1=v1)
+        o1, o2 = oracle.decompose(A, v1=v1)
+        assert np.array_equal(a1, r1) and np.array_equal(a2, r2)
+        assert np.array_equal(o1, r1) and np.array_equal(o2, r2)
+    capfd.readouterr()
+
+
 def test_decompose_cxx_entry_points(sp):
     """decompose / decompose_v1 with the reference's C++ signatures (include/spmm_decompose.h) agree with the C ABI."""
     import ctypes

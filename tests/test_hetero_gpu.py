@@ -24,7 +24,7 @@ def run_hetero(sp, torch, A1, A2, B_bits, M, N, K, split_k, workspace=True):
     wd = od = None
     if A2 is not None:
         words, offsets, _ = sp.InitSparseMatrixA_API(A2, M, N, K)
-        wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+        wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
         od = torch.from_numpy(offsets).to(dev)
     Bd = torch.from_numpy(np.ascontiguousarray(B_bits).view(np.int16)).to(dev)
     Cd = torch.full((M, N), 0x7E00, dtype=torch.int16, device=dev)
@@ -155,7 +155,7 @@ def test_error_paths(sp, torch_cuda):
     Bd = torch.zeros((K, N), dtype=torch.int16, device=dev)
     Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
     words, offsets, _ = sp.InitSparseMatrixA_API(A1, M, N, K)
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
     od = torch.from_numpy(offsets).to(dev)
     # unsupported N: the reference's message and cudaErrorUnknown
     assert sp.SpMM_SplitK_API(None, vd, None, None, md, None, Bd, Cd, M, 24, K, None, 1) == 999

@@ -20,7 +20,7 @@ def torch_cuda():
 
 def run_spmm(sp, torch, words, offsets, B_bits, M, N, K, split_k, workspace=True):
     dev = torch.device("cuda:0")
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
     od = torch.from_numpy(offsets).to(dev)
     Bd = torch.from_numpy(np.ascontiguousarray(B_bits).view(np.int16)).to(dev)
     Cd = torch.full((M, N), 0x7E00, dtype=torch.int16, device=dev)  # NaN pattern: unwritten rows show up
@@ -158,7 +158,7 @@ def test_error_paths(sp, torch_cuda, capfd):
     M, K, N = 256, 128, 16
     A = sp.synth_fp16((M, K), 61, 0.02, 0.8)
     words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
     od = torch.from_numpy(offsets).to(dev)
     Bd = torch.zeros((K, 64), dtype=torch.int16, device=dev)
     Cd = torch.zeros((M, 64), dtype=torch.int16, device=dev)
@@ -188,7 +188,7 @@ def test_token_major_layout(sp, oracle, torch_cuda, case):
     A = sp.synth_fp16((M, K), 300 + N, 0.02, p)
     B = sp.synth_fp16((K, N), 400 + N, 1.0, 0.0)
     words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
     od = torch.from_numpy(offsets).to(dev)
     Bt = torch.from_numpy(np.ascontiguousarray(B.T).view(np.int16)).to(dev)          # [N][K]
     Ct = torch.full((N, M), 0x7E00, dtype=torch.int16, device=dev)                   # [N][M]
@@ -258,7 +258,7 @@ def test_host_buffer_entry_point(sp, oracle, torch_cuda):
     B = sp.synth_fp16((K, N), 902, 1.0, 0.0)
     words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
     want = run_spmm(sp, torch, words, offsets, B, M, N, K, sk)
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
     od = torch.from_numpy(offsets).to(dev)
     B_host = torch.from_numpy(B.view(np.int16)).pin_memory()
     C_host = torch.zeros((M, N), dtype=torch.int16).pin_memory()
@@ -287,3 +287,37 @@ def test_a_wait_that_runs_out_is_reported_not_hung(sp, oracle, torch_cuda):
     words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
     C = run_spmm(sp, torch, words, offsets, B, M, N, K, 4)
     assert oracle.tolerance_check(C, oracle.spmm_f64(A, B))[0]
+
+
+def test_weights_written_by_the_preceding_kernel(sp, oracle, torch_cuda):
+    """The SpMM is launched so that it may start while its stream predecessor drains.  By default it reads
+    nothing before that predecessor has completed, so weights (and offsets) produced by the kernel directly
+    ahead of it -- here an elementwise kernel that fills the buffers -- are seen in full."""
+    torch = torch_cuda
+    dev = torch.device("cuda:0")
+    assert sp.set_weights_constant(False) in (True, False)
+    M, K, N = 4608, 9216, 16
+    A = sp.synth_fp16((M, K), 111, 0.02, 0.8)
+    B = sp.synth_fp16((K, N), 112, 1.0, 0.0)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    src_w = torch.from_numpy(words.view(np.int32)).to(dev)
+    src_o = torch.from_numpy(offsets).to(dev)
+    Bd = torch.from_numpy(B.view(np.int16)).to(dev)
+    ws = torch.zeros(sp.workspace_bytes(M, N, 8) // 2, dtype=torch.int16, device=dev)
+    want = None
+    for attempt in range(3):
+        wd = torch.zeros_like(src_w)      # all-zero words: every value lands on position 0 with value 0
+        od = torch.zeros_like(src_o)
+        Cd = torch.full((M, N), 0x7E00, dtype=torch.int16, device=dev)
+        torch.cuda.synchronize()
+        torch.add(src_o, 0, out=od)       # kernels on the same stream, directly ahead of the SpMM
+        torch.add(src_w, 0, out=wd)
+        assert sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 8) == 0
+        torch.cuda.synchronize()
+        assert sp.device_status() == 0
+        C = Cd.cpu().numpy().view(np.uint16)
+        if want is None:
+            ok, max_ratio, mean_rel = oracle.tolerance_check(C, oracle.spmm_f64_threads(A, B))
+            assert ok, (max_ratio, mean_rel)
+            want = C
+        assert np.array_equal(C, want), "attempt %d" % attempt

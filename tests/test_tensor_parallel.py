@@ -54,7 +54,7 @@ if mode == "column":
         dev = torch.device("cuda", rank)
         Cd = torch.zeros((m, N), dtype=torch.int16, device=dev)
         ws = torch.zeros(sp.workspace_bytes(m, N, 8) // 2, dtype=torch.int16, device=dev)
-        rc = sp.SpMM_SplitK_API(None, None, torch.from_numpy(np.concatenate([w, np.zeros(4, np.uint32)]).view(np.int32)).to(dev), None, None,
+        rc = sp.SpMM_SplitK_API(None, None, torch.from_numpy(w.view(np.int32)).to(dev), None, None,
                                 torch.from_numpy(o).to(dev), torch.from_numpy(B.view(np.int16)).to(dev), Cd, m, N, K, ws, 8)
         torch.cuda.synchronize(); assert rc == 0 and sp.device_status() == 0
         mine = Cd.cpu().numpy().view(np.uint16)
@@ -72,8 +72,8 @@ else:
     w, o, _ = sp.InitSparseMatrixA_API(As, M, N, k)
     if backend == "nccl":
         dev = torch.device("cuda", rank)
-        layer = tp.RowParallelSpMM(torch.from_numpy(np.concatenate([w, np.zeros(4, np.uint32)]).view(np.int32)).to(dev),
-                                   torch.from_numpy(o).to(dev), M, N, k, reduce="peer" if mode == "row_peer" else "nccl")
+        layer = tp.RowParallelSpMM(torch.from_numpy(w.view(np.int32)).to(dev),
+                                   torch.from_numpy(o).to(dev), M, N, k, reduce="peer" if mode == "row_peer" else "nccl")  # row_peer_graph starts from the NCCL answer
         Bd = torch.from_numpy(Bs.view(np.int16)).to(dev)
         C = layer.forward(Bd)
         torch.cuda.synchronize(); assert sp.device_status() == 0
@@ -86,6 +86,26 @@ else:
             torch.cuda.synchronize()
             assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
             assert np.array_equal(again.cpu().numpy().view(np.uint16), total)
+        if mode == "row_peer_graph":
+            # the replayable form (epoch kept on the device): two layers whose reductions alternate, captured
+            # once in a CUDA graph and replayed; every replay must give the un-captured answer
+            layers = [tp.RowParallelSpMM(layer.words, layer.offsets, M, N, k, reduce="peer", replayable=True) for _ in range(2)]
+            for L in layers:
+                L.forward(Bd)
+            torch.cuda.synchronize()
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    outs = [L.forward(Bd) for L in layers]
+                for replay in range(6):
+                    for out in outs:
+                        out.zero_()
+                    g.replay()
+                    torch.cuda.synchronize()
+                    for out in outs:
+                        assert np.array_equal(out.cpu().numpy().view(np.uint16), total), replay
+            assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
     else:
         part = torch.from_numpy(oracle.spmm_from_csl(w, o, Bs, M, k).view(np.float16).astype(np.float32))
         total = tp.all_reduce_partial(part).numpy().astype(np.float16).view(np.uint16)
@@ -118,7 +138,7 @@ def test_two_gloo_ranks_on_cpu(mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["column", "row", "row_peer"])
+@pytest.mark.parametrize("mode", ["column", "row", "row_peer", "row_peer_graph"])
 def test_two_nccl_ranks_on_gpus(mode):
     import torch
     if torch.cuda.device_count() < 2:

@@ -23,7 +23,7 @@ def test_own_scratch_matches_workspace_entry_point(sp, shape):
     M, K, N = shape
     A = sp.synth_fp16((M, K), 71 + N, 0.02, 0.8)
     words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
-    wd = torch.from_numpy(np.concatenate([words, np.zeros(4, np.uint32)]).view(np.int32)).to(dev)
+    wd = torch.from_numpy((words if words.size else np.zeros(4, np.uint32)).view(np.int32)).to(dev)
     od = torch.from_numpy(offsets).to(dev)
     ws = torch.zeros(sp.workspace_bytes(M, N, 16) // 2, dtype=torch.int16, device=dev)
     for call in range(2):
