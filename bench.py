@@ -153,6 +153,7 @@ class Layer:
             d0 = torch.from_numpy(A.view(np.float16)).to(dev)
             self.dense = [d0] + [d0.clone() for _ in range(dense_copies - 1)]
         self.peer = None      # two PeerAllReduce objects used alternately (row-parallel layers, world > 1)
+        self.fused = None     # FusedRowParallelSpMM: the sum over ranks inside the SpMM kernel
         self.result = self.C  # where the layer's final result lies after a step
 
     def launch(self, sp, copy, C=None):
@@ -244,6 +245,7 @@ def run_ours(args):
         for L in some_layers:
             if L.split == "cols":
                 L.peer = [tp.PeerAllReduce(L.M * N, dev, replayable=True) for _ in range(2)]
+                L.fused = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k)
 
     layers = build(LAYERS, 0, True)
     # ---- the sum over ranks of the layers split by K: NCCL all-reduce, and the library's own kernel
@@ -256,13 +258,16 @@ def run_ours(args):
             if rank == 0:
                 print("peer-memory reduction unavailable:", exc, file=sys.stderr)
         peer_ok = reduce_sum([1.0 if peer_ok else 0.0])[0] == world
-    modes = ["none"] if world == 1 else (["peer", "nccl", "none"] if peer_ok else ["nccl", "none"])
+    # "fused": sum over ranks inside the SpMM kernel; "peer": a second kernel over peer memory; "nccl": all-reduce
+    modes = ["none"] if world == 1 else (["fused", "peer", "nccl", "none"] if peer_ok else ["nccl", "none"])
     main_mode = modes[0]
 
     def run_layer(L, copy, mode, use):
         """SpMM of layer L (+ the sum over ranks for a layer split by K).  `use`: running count of uses of L, for the
         alternation between its two peer-reduction objects."""
-        if L.split == "cols" and mode == "peer":
+        if L.split == "cols" and mode == "fused":
+            L.result = L.fused.forward(L.B, words=L.words[copy % len(L.words)]).view(torch.int16)
+        elif L.split == "cols" and mode == "peer":
             red = L.peer[use & 1]
             L.launch(sp, copy, red.next_buffer().view(torch.int16).view(L.M, N))
             L.result = red.reduce().view(torch.int16).view(L.M, N)
@@ -303,6 +308,15 @@ def run_ours(args):
                 time_launches(stream, lambda i: torch.matmul(L.dense[i % len(L.dense)], Bh, out=out), count_d), 2)
             entry["speedup_vs_cublas"] = round(entry["cublas_dense_us"] / entry["spmm_us"], 3)
         entry["roofline_frac"] = round(L.algo_bytes / entry["spmm_us"] / 1e3 / hbm_peak, 4)
+        entry["hbm_floor_us"] = round(L.algo_bytes / hbm_peak / 1e3, 2)
+        if L.split == "cols" and world > 1:
+            best = min(entry["spmm_plus_%s_reduce_us" % mode] for mode in modes[:-1])
+            entry["limited_by"] = ("sum over ranks: +%.1f us on a %.1f us product (HBM floor %.1f us)"
+                                   % (best - entry["spmm_us"], entry["spmm_us"], entry["hbm_floor_us"]))
+        else:
+            entry["limited_by"] = ("fixed cost of a launch (prologue, ramp-up, tail): %.1f us against an HBM floor of %.1f us"
+                                   % (entry["spmm_us"], entry["hbm_floor_us"])
+                                   if entry["roofline_frac"] < 0.45 else "decode work per tile in shared memory")
         return entry
 
     def verify(some_layers, mode, seed):
@@ -443,8 +457,8 @@ def run_ours(args):
     value = weight_bytes / (ms_per_step * 1e-3) / 1e9
     achieved = algo_bytes / world / (ms_per_step * 1e-3) / 1e9  # per GPU: the roofline is a per-GPU figure
     launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode == "peer" else 0)
-    reduce_note = {"none": "no collective (one GPU)", "peer": "library kernel over peer memory (NVLink loads, no multicast)",
-                   "nccl": "NCCL all-reduce"}[main_mode]
+    reduce_note = {"none": "no collective (one GPU)", "fused": "inside the SpMM kernel, plain NVLink peer loads",
+                   "peer": "library kernel over peer memory (plain NVLink peer loads)", "nccl": "NCCL all-reduce"}[main_mode]
     line = {
         "metric": METRIC,
         "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -763,6 +777,99 @@ def run_prefill(args):
     assert sp.device_status() == 0
 
 
+class quiet_stdout:
+    """Silences what C code prints to stdout (the reference's encoders report statistics with printf)."""
+
+    def __enter__(self):
+        sys.stdout.flush()
+        self.saved = os.dup(1)
+        self.null = os.open(os.devnull, os.O_WRONLY)
+        os.dup2(self.null, 1)
+
+    def __exit__(self, *exc):
+        import ctypes
+        ctypes.CDLL(None).fflush(None)
+        os.dup2(self.saved, 1)
+        os.close(self.saved)
+        os.close(self.null)
+
+
+def reference_sparse_tensor_core_kernel(sp, torch, dev, A1_bits, B_bits, split_k, reps=20):
+    """The reference's own GPU kernel for the 2:4 half (csrc/SpMM_Kernel.cuh:293-735: mma.sp.m16n8k16 with fp16
+    accumulators), compiled unchanged for sm_100a into oracle/_ref, fed with the A1 vectors, index words and
+    metadata of InitSparseMatrixA1_Vec_Sparse_Load / inspect_metadata (this library's, bit-identical to the
+    reference's), followed by the sum of its Split_K fp16 slabs (the reference leaves that to the harness's Reduction
+    kernel, kernel_benchmark/FSP_Batch8.h:209-229; a torch reduction stands in for it).  Returns
+    (microseconds per product or None, note, result as a float32 tensor or None)."""
+    import ctypes
+    path = os.path.join(ROOT, "oracle", "_ref", "libSpMM_API_ref.so")
+    if not os.path.exists(path):
+        return None, "unavailable: oracle/_ref/libSpMM_API_ref.so was not built", None
+    try:
+        ref = ctypes.CDLL(path)
+        spmm = getattr(ref, "_Z15SpMM_SplitK_APIP11CUstream_stPK6__halfPK5uint4PKmPKiSA_S3_PS1_iiiSB_i")
+    except (OSError, AttributeError) as exc:
+        return None, "unavailable: %s" % exc, None
+    spmm.argtypes = [ctypes.c_void_p] * 8 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int]
+    spmm.restype = ctypes.c_int
+    M, K = A1_bits.shape
+    N = B_bits.shape[1]
+    if M % 256 or K % 64 or N not in (8, 16, 32, 64):
+        return None, "unavailable: the reference kernel needs M %% 256 == 0, K %% 64 == 0, N in {8,16,32,64}", None
+    lib = sp.spmm_api.LIB
+    u16p, u64p, i32p = ctypes.POINTER(ctypes.c_uint16), ctypes.POINTER(ctypes.c_uint64), ctypes.POINTER(ctypes.c_int)
+    enc = getattr(lib, "_Z34InitSparseMatrixA1_Vec_Sparse_LoadP6__halfiiPS0_PPmPPi")
+    enc.argtypes = [u16p, ctypes.c_int, ctypes.c_int, ctypes.POINTER(u16p), ctypes.POINTER(u64p), ctypes.POINTER(i32p)]
+    enc.restype = ctypes.c_int
+    meta_fn = getattr(lib, "_Z16inspect_metadataP6__halfPiii")
+    meta_fn.argtypes = [u16p, i32p, ctypes.c_int, ctypes.c_int]
+    meta_fn.restype = None
+    A1 = np.ascontiguousarray(A1_bits, dtype=np.uint16)
+    vp, ip, op = u16p(), u64p(), i32p()
+    meta = np.zeros((M // 16) * (K // 16) * 8, np.int32)
+    with quiet_stdout():
+        n_off = enc(A1.ctypes.data_as(u16p), M, K, ctypes.byref(vp), ctypes.byref(ip), ctypes.byref(op))
+        meta_fn(A1.ctypes.data_as(u16p), meta.ctypes.data_as(i32p), M, K)
+    offsets = np.ctypeslib.as_array(op, shape=(n_off,)).copy()
+    vectors = int(offsets[-1])
+    values = np.ctypeslib.as_array(vp, shape=(vectors * 8,)).copy()
+    index = np.ctypeslib.as_array(ip, shape=(vectors,)).copy()
+    for ptr in (vp, ip, op):
+        lib.spmm_b200_free(ctypes.cast(ptr, ctypes.c_void_p))
+    if np.any(np.diff(offsets[:-1]) <= 0):
+        return None, "unavailable: an empty 256 x 64 tile (the reference encoder mis-sizes those, csrc/SpMM_API.cu:1202)", None
+    vd = torch.from_numpy(values.view(np.int16)).to(dev)
+    xd = torch.from_numpy(index.view(np.int64)).to(dev)
+    md = torch.from_numpy(meta).to(dev)
+    od = torch.from_numpy(offsets).to(dev)
+    Bd = torch.from_numpy(np.ascontiguousarray(B_bits).view(np.int16)).to(dev)
+    ws = torch.zeros((split_k, M, N), dtype=torch.float16, device=dev)
+    out = torch.empty((M, N), dtype=torch.float16, device=dev)
+    stream = ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+    def once():
+        rc = spmm(stream, None, vd.data_ptr(), xd.data_ptr(), md.data_ptr(), od.data_ptr(), Bd.data_ptr(), None, M, N, K,
+                  ws.data_ptr(), split_k)
+        torch.sum(ws, dim=0, dtype=torch.float16, out=out)
+        return rc
+
+    rc = once()
+    torch.cuda.synchronize()
+    if rc != 0:
+        return None, "unavailable: the reference launch returned cudaError %d" % rc, None
+    for _ in range(3):
+        once()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        once()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / reps, "Split_K %d, fp16 accumulate, torch sum of the slabs included" % split_k, out.float()
+
+
+
 def prune_2_of_4(A_bits, keep_prob, seed):
     """2:4 magnitude pruning along K, then each survivor is zeroed with probability 1 - keep_prob."""
     groups = np.abs(A_bits.view(np.float16).astype(np.float32)).reshape(-1, 4)
@@ -811,10 +918,23 @@ def run_hetero(args):
             torch.cuda.synchronize()
         return e0.elapsed_time(e1) * 1000.0 / (reps * 2 * copies)
 
-    Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB400, 1.0).view(np.int16)).to(dev)
+    B_bits = sp.synth_fp16((K, N), 0xB400, 1.0)
+    Bd = torch.from_numpy(B_bits.view(np.int16)).to(dev)
     Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
     ws = torch.zeros(sp.workspace_bytes(M, N, 8) // 2, dtype=torch.int16, device=dev)
     copies = 2  # rotate over two copies of the weights: more than L2 holds
+
+    # The reference's own kernel for the structured half, first on a 512 x 256 case checked against an fp64
+    # product; the full-size case runs only if that one came out right.
+    small_A = prune_2_of_4(sp.synth_fp16((512, 256), 0xA410, 0.02, 0.0), 0.5, 5)
+    small_B = sp.synth_fp16((256, N), 0xB410, 1.0)
+    ref_us, ref_note, ref_C = reference_sparse_tensor_core_kernel(sp, torch, dev, small_A, small_B, 2, reps=3)
+    reference_kernel_ok = False
+    if ref_C is not None:
+        want = torch.from_numpy(small_A.view(np.float16)).to(dev).double() @ torch.from_numpy(small_B.view(np.float16)).to(dev).double()
+        err = float((ref_C.double() - want).abs().max() / want.abs().max())
+        reference_kernel_ok = err <= 2e-2  # fp16 accumulation: looser than the product's own gate
+        ref_note = ref_note if reference_kernel_ok else "unavailable: wrong result on the 512 x 256 check (max err / max|C| = %.3g)" % err
     for label, make in (("2:4 pruned, half of the survivors zeroed (75 % sparse)",
                          lambda: prune_2_of_4(sp.synth_fp16((M, K), 0xA400, 0.02, 0.0), 0.5, 4)),
                         ("i.i.d. 80 % sparse", lambda: sp.synth_fp16((M, K), 0xA401, 0.02, 0.8))):
@@ -852,7 +972,23 @@ def run_hetero(args):
         t_csl = timed(csl, copies)
         t_dense = timed(lambda i: torch.matmul(Ad[i % copies], Bh), copies)
         algo = a1_bytes + residual_bytes + 2 * K * N + 2 * M * N
-        print(json.dumps({"input": label, "M": M, "K": K, "N": N, "residual_nnz": residual_nnz,
+        reference_kernel = {"reference_kernel": ref_note}
+        if reference_kernel_ok and residual_nnz == 0:
+            # the structured half alone, as the reference's harness times its A1 kernel (kernel_benchmark/spmm_test.cu:467-506)
+            us, note, C_ref = reference_sparse_tensor_core_kernel(sp, torch, dev, A1, B_bits, 9)
+            reference_kernel = {"reference_kernel": note}
+            if us is not None:
+                hetero(0)
+                torch.cuda.synchronize()
+                ours = Cd.view(torch.float16).float()
+                reference_kernel.update({"reference_kernel_us": round(us, 2),
+                                         "speedup_vs_reference_kernel": round(us / t_hetero, 3),
+                                         "reference_kernel_max_diff_over_max_c": float("%.3g" % float(
+                                             (C_ref - ours).abs().max() / ours.abs().max()))})
+        elif reference_kernel_ok:
+            reference_kernel = {"reference_kernel": "not run: this input has a residual, which the reference multiplies with "
+                                                    "separate CUDA-core kernels that are not part of its library"}
+        print(json.dumps({"input": label, "M": M, "K": K, "N": N, "residual_nnz": residual_nnz, **reference_kernel,
                           "hetero_us": round(t_hetero, 2), "tiled_csl_only_us": round(t_csl, 2),
                           "cublas_dense_us": round(t_dense, 2),
                           "a1_bytes": a1_bytes, "residual_bytes": residual_bytes, "tiled_csl_bytes": csl_bytes,

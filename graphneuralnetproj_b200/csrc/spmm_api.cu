@@ -19,36 +19,21 @@ namespace {
 
 // Shape of the block per width of the B slice (bounded by 227 KB of shared memory and 512 TMEM
 // columns): D decoder teams of WPT warps, Q MMA-issuing warps, S ring slots, VPL 4-word vectors
-// held per lane (WPT * VPL * 32 vectors = 7168 bytes of words in flight per team).
+// held per lane (WPT * VPL * 32 vectors = 7168 bytes of words in flight per team, loaded straight into
+// registers: staging them through shared memory by bulk copy was measured 2-7 % slower at every width).
 // Up to 64 columns the kernel is bound by decoding; 128 and 256 columns serve prefill sizes, where a
 // decoded tile feeds four 128 x N x 16 MMAs of 64-128 cycles each and fewer, wider slots are enough.
-#ifndef SPMM_B200_D16
-#define SPMM_B200_D16 8
-#endif
-#ifndef SPMM_B200_S16
-#define SPMM_B200_S16 8
-#endif
-#ifndef SPMM_B200_BM16
-#define SPMM_B200_BM16 2
-#endif
 template<int N>
 struct DecodeConfig {
-    static constexpr int D    = N == 16 ? (SPMM_B200_D16) : (N <= 64 ? 8 : 4);   // decoder teams
+    static constexpr int D    = N <= 64 ? 8 : 4;   // decoder teams
     static constexpr int WPT  = N <= 64 ? 1 : 2;   // warps per team
     static constexpr int Q    = N <= 64 ? 4 : (N == 128 ? 2 : 1);  // MMA-issuing warps (2 * Q * N TMEM columns)
     static constexpr int VPL  = 14 / WPT;
-    static constexpr int S    = N == 16 ? (SPMM_B200_S16) : (N <= 64 ? 8 : (N == 128 ? 6 : 4));  // ring slots
-    // vectors per lane that are staged through shared memory by bulk copy (the rest are loaded straight
-    // into registers); none at N = 64, where staging buffers do not fit beside eight 16 KB A buffers
-    // and eight 8 KB B slices
-#ifndef SPMM_B200_VS16
-#define SPMM_B200_VS16 VPL
-#endif
-    static constexpr int VS   = N == 64 ? 0 : (N == 16 ? (SPMM_B200_VS16) : VPL);
+    static constexpr int S    = N <= 64 ? 8 : (N == 128 ? 6 : 4);  // ring slots
     // B slices (row-major layout): tiled TMA loads, issued by the MMA warps a lap ahead into a second
     // B buffer where that fits in shared memory (N <= 16), else by the tile's decoder
     // (N = 8 keeps the 16-byte copies: its staged rows are twice as wide as the rows of B)
-    static constexpr int BM   = N == 8 ? 0 : (N == 16 ? (SPMM_B200_BM16) : 1);
+    static constexpr int BM   = N == 8 ? 0 : (N == 16 ? 2 : 1);
 };
 
 struct DeviceInfo {
@@ -131,9 +116,9 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     constexpr int D    = Cfg::D;
     constexpr int BM   = TM ? 0 : Cfg::BM;  // token-major B keeps the 16-byte copies
     constexpr int smem =
-        decode_smem_bytes<NB, Cfg::S, BM, word_stage_bytes<D, Cfg::WPT, Cfg::VS>()>();
+        decode_smem_bytes<NB, Cfg::S, BM>();
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, Cfg::S, TM, Cfg::VS, BM>;
+    auto kern = spmm_decode_kernel<N, D, Cfg::Q, Cfg::WPT, Cfg::VPL, Cfg::S, TM, BM>;
     {
         std::lock_guard<std::mutex> guard(g_device_lock);
         if (!dev.attrs_set[n_index]) {
@@ -261,7 +246,7 @@ namespace {
 // Shared by both layouts: validates, partitions, launches.  token_major: B[N][K], C[N][M].
 cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const int* TileOffsets, const half* B, half* C,
                            int M_Global, int N_Global, int K_Global, half* Reduction_Workspace, int Split_K, bool token_major,
-                           const float* addend = nullptr, size_t workspace_skip_bytes = 0)
+                           const float* addend = nullptr, size_t workspace_skip_bytes = 0, const PeerSumParams* peer = nullptr)
 {
     // N: 8, 16, 32, 64 as in the reference (csrc/SpMM_API.cu:105-196); multiples of 64 beyond that are
     // served by the same kernel, one 64-column block per blockIdx.y (row-major layout only).
@@ -320,6 +305,11 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
         }
     }
     params.weights_early = g_weights_constant.load(std::memory_order_relaxed);
+    if (peer != nullptr) {
+        if (wide || token_major)
+            return cudaErrorInvalidValue;
+        params.peer = *peer;
+    }
     params.addend       = addend;
     params.n            = N_Global;
     params.tiles_k      = tiles_k;
@@ -764,6 +754,52 @@ int spmm_b200_spmm_splitk_host_io_batch(void* stream, int count, const spmm_b200
     SPMM_B200_TRY(cudaStreamWaitEvent(st, lanes->joined, 0));
 #undef SPMM_B200_TRY
     return static_cast<int>(cudaSuccess);
+}
+
+int spmm_b200_spmm_row_parallel(void*        stream,
+                                const void*  Compressed_A,
+                                const int*   TileOffsets,
+                                const void*  B,
+                                void*        C,
+                                int          M_Global,
+                                int          N_Global,
+                                int          K_Global,
+                                void*        Reduction_Workspace,
+                                int          Split_K,
+                                void* const* partial_buffers,
+                                void* const* flag_arrays,
+                                int          rank,
+                                int          world,
+                                void*        state,
+                                unsigned     limit_ms)
+{
+    using namespace spmm_b200;
+    if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || !partial_buffers || !flag_arrays || !state
+        || (reinterpret_cast<uintptr_t>(state) & 3u))
+        return static_cast<int>(cudaErrorInvalidValue);
+    if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64) {
+        printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
+        return static_cast<int>(cudaErrorUnknown);
+    }
+    PeerSumParams peer;
+    for (int r = 0; r < world; r++) {
+        for (int parity = 0; parity < 2; parity++) {
+            void* buffer = partial_buffers[parity * world + r];
+            if (!buffer || (reinterpret_cast<uintptr_t>(buffer) & 15u))
+                return static_cast<int>(cudaErrorInvalidValue);
+            peer.partial[parity][r] = static_cast<half*>(buffer);
+        }
+        if (!flag_arrays[r] || (reinterpret_cast<uintptr_t>(flag_arrays[r]) & 3u))
+            return static_cast<int>(cudaErrorInvalidValue);
+        peer.flags[r] = static_cast<uint32_t*>(flag_arrays[r]);
+    }
+    peer.state    = static_cast<uint32_t*>(state);
+    peer.rank     = rank;
+    peer.world    = world;
+    peer.limit_ns = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
+    return static_cast<int>(spmm_tiled_csl(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A), TileOffsets,
+                                           static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global, K_Global,
+                                           static_cast<half*>(Reduction_Workspace), Split_K, false, nullptr, 0, &peer));
 }
 
 int spmm_b200_spmm_splitk_token_major(void*       stream,

@@ -23,12 +23,10 @@
 //                   for the words two laps ahead to be brought into L2.
 //   warps 4+Q..     decoders: D teams of WPT warps; team t restores tiles t, t + D, ...
 //                   of the chunk into slot (tile % S).  Per tile a team
-//                     - receives the first part of the tile's words in its staging buffer
-//                       (one bulk copy, issued a whole tile ahead, completion on an
-//                       mbarrier) and reads them into registers; the buffer goes back to
-//                       the copy engine at once for the team's next tile; the rest of the
-//                       words come by 128-bit streaming loads straight into registers,
-//                       issued as soon as the previous tile has been scattered,
+//                     - holds the tile's words in registers: 128-bit streaming loads, issued
+//                       as soon as the previous tile has been scattered, without a branch
+//                       around them so that they pipeline (the words were asked into L2
+//                       two laps earlier),
 //                     - waits until the tensor core has finished with the slot,
 //                     - clears the A buffer with 128-bit stores,
 //                     - scatters the values to the half-word positions the words carry,
@@ -47,8 +45,6 @@
 // a block-wide abort word, all roles fall through to the common exit, TMEM is
 // released and a status word in global memory records the event.
 #pragma once
-
-#include <type_traits>
 
 #include <cuda.h>
 #include <cuda_fp16.h>
@@ -75,6 +71,24 @@ enum DeviceStatus : int { kStatusOk = 0, kStatusWaitTimeout = 1, kStatusBadInput
 __device__ unsigned int g_row_arrivals[kCounterSets][kMaxRowTiles * kEpilogueWarps];
 __device__ int          g_device_status;
 
+constexpr int kMaxPeers = 8;  // ranks of a row-parallel (split by K) layer whose sum is folded into the epilogue
+
+// Sum over the ranks of a layer split by K, folded into the SpMM's epilogue (no counterpart in the
+// reference, which is single-GPU; its FasterTransformer glue all-reduces with NCCL after the product).
+// Every rank writes its finished rows to its own partial buffer instead of C, tells every peer row of
+// tiles by row of tiles (one flag per quarter of a row of tiles and sender, carrying the call's epoch),
+// and once a block has finished its own tiles it takes rows of tiles in turn, waits for all ranks'
+// flags and adds the ranks' partial rows in rank order out of the peers' memory (plain loads over
+// NVLink).  Epochs only grow, so nothing is reset; the partial buffers alternate with the epoch's
+// parity, so a fast rank's next product never overwrites what a slow peer is still reading.
+struct PeerSumParams {
+    half*     partial[2][kMaxPeers] = {};  // [epoch parity][rank]: that rank's partial result [M][N], mapped here
+    uint32_t* flags[kMaxPeers]      = {};  // flags[r]: rank r's flag array, (M / 128) * 4 * world words
+    uint32_t* state                 = nullptr;  // this rank's: [0] epoch of the previous call, [1] blocks finished
+    int       rank = 0, world = 0;              // world == 0: no sum over ranks
+    unsigned long long limit_ns = 0;
+};
+
 struct DecodeParams {
     const uint4* words        = nullptr;  // tiled-CSL words, viewed as 4-word vectors
     const int*   tile_offsets = nullptr;  // vectors before each tile
@@ -95,6 +109,7 @@ struct DecodeParams {
     // B as a 2-D tensor [K][ld] of halves, boxes of 64 k rows x min(N, 64) columns in the swizzle mode of
     // the staged layout: for the forms whose B slices arrive by tiled TMA loads (BM != 0)
     alignas(64) CUtensorMap b_map;
+    PeerSumParams peer;
     Schedule     sched;
 };
 
@@ -126,19 +141,11 @@ struct BTile {
     }
 };
 
-// Per ring slot one A buffer and BBUF B buffers; STAGE bytes of word staging buffers (0 when the
-// words are loaded straight into registers).
-template<int NB, int S, int BM, int STAGE>
+// Per ring slot one A buffer and one or two (BM == 2) B buffers.
+template<int NB, int S, int BM>
 constexpr int decode_smem_bytes()
 {
-    return 1024 + S * (kATileBytes + (BM == 2 ? 2 : 1) * BTile<NB>::kBytes) + STAGE + 512;
-}
-
-// Staging bytes for D decoder teams that each stage WPT * VS * 32 vectors of 16 bytes.
-template<int D, int WPT, int VS>
-constexpr int word_stage_bytes()
-{
-    return D * WPT * VS * 32 * 16;
+    return 1024 + S * (kATileBytes + (BM == 2 ? 2 : 1) * BTile<NB>::kBytes) + 512;
 }
 
 template<int D, int Q, int WPT>
@@ -188,17 +195,11 @@ __device__ __forceinline__ void scatter_vector(uint8_t* tile, const uint4& w, bo
 // TM   : 1 = token-major activations and results, B[N][K] and C[N][M] (the layout of the upstream
 //        library and of its FasterTransformer caller, third_party/ft.patch:2822-2846): the B slice of a
 //        k tile is then K-contiguous and is staged in the same 128-byte-swizzle layout as A.
-// VS   : how many of a lane's VPL vectors travel global -> shared memory by bulk copy (one staging
-//        buffer of VS * WPT * 32 vectors per team) and are then read into registers; the other
-//        VPL - VS are 128-bit streaming loads straight into registers, issued a tile ahead.
-//        Register loads are tracked in L1, whose size (what the shared memory carve-out leaves) bounds
-//        their bytes in flight; bulk copies have no such bound but the copy engine moves only about
-//        25 bytes per clock into an SM's shared memory.  Splitting a tile between the two paths uses both.
 // BM   : how a tile's B slice reaches shared memory.  0: 16-byte async copies by the tile's decoders,
 //        1: tiled TMA loads issued by one of them, both once the slot has been handed back (one B
 //        buffer per slot); 2: tiled TMA loads issued by the MMA warp one lap ahead into the other of
 //        two B buffers per slot (the decoders never touch B).  1 and 2 need p.b_map and row-major B.
-template<int N, int D, int Q, int WPT, int VPL, int S, int TM, int VS, int BM>
+template<int N, int D, int Q, int WPT, int VPL, int S, int TM, int BM>
 __global__ void __launch_bounds__(decode_threads<D, Q, WPT>(), 1)
 spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 {
@@ -209,18 +210,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const uint32_t a_base    = smem_base;
     const uint32_t b_base    = a_base + S * kATileBytes;
-    const uint32_t w_base    = b_base + BBUF * S * BT::kBytes;  // word staging, one buffer per team
-    constexpr bool WTMA        = VS > 0;
-    constexpr int  kStageBytes = WPT * VS * 32 * 16;
-    static_assert(VS >= 0 && VS <= VPL, "a lane cannot stage more vectors than it holds");
-    const uint32_t bar_base  = w_base + D * kStageBytes;
-    // barrier map (8 bytes each): [0,S) tile full, [S,2S) tile free, acc full x2, acc free x2, [.., +D) words full
+    const uint32_t bar_base  = b_base + BBUF * S * BT::kBytes;
+    // barrier map (8 bytes each): [0,S) tile full, [S,2S) tile free, acc full x2, acc free x2
     auto tile_full  = [&](int s) { return bar_base + 8u * s; };
     auto tile_free  = [&](int s) { return bar_base + 8u * (S + s); };
     auto acc_full   = [&](int b) { return bar_base + 8u * (2 * S + b); };
     auto acc_free   = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
-    auto words_full = [&](int t) { return bar_base + 8u * (2 * S + 4 + t); };
-    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4 + D);
+    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * S + 4);
     uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
     volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
@@ -242,15 +238,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     static_assert(S % Q == 0, "a ring slot must always be served by the same MMA warp (barrier phases alias otherwise)");
     static_assert(S >= D, "every team needs a slot of its own to start with");
     static_assert(BM == 0 || !TM, "tiled loads of B are for the row-major layout");
-    static_assert(8 * (2 * S + 4 + D) + 8 <= 512, "barrier block");
+    static_assert(8 * (2 * S + 4) + 8 <= 512, "barrier block");
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; s++) {
             ptx::mbar_init(tile_full(s), WPT);
             ptx::mbar_init(tile_free(s), 1);
         }
-        for (int t = 0; t < D; t++)
-            ptx::mbar_init(words_full(t), 1);
         for (int b = 0; b < 2; b++) {
             ptx::mbar_init(acc_full(b), Q);
             ptx::mbar_init(acc_free(b), kEpilogueWarps);
@@ -340,53 +334,20 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         uint4        r[VPL];                     // this warp's share of the tile's words
         int          nvec = 0, next0 = 0, next1 = 0;
         int          j    = (tile_begin + s_own) % tiles_k;
-        // Register loads of vectors V0 .. VPL - 1 of this lane from `from` (this lane's vector 0 of the
-        // batch).  No branch per load (loads inside branches do not pipeline): a lane whose vector lies
-        // beyond the batch's `count` reads the batch's last vector instead and never scatters it.
-        auto load_words = [&](const uint4* from, int count, auto first_vector) {
-            constexpr int V0 = decltype(first_vector)::value;
+        // Register loads of this lane's VPL vectors of a batch from `from` (the lane's first vector).  No
+        // branch per load (loads inside branches do not pipeline: 11 against 2.8 cycles each): a lane whose
+        // vector lies beyond the batch's `count` reads the batch's last vector instead and never scatters it.
+        auto load_words = [&](const uint4* from, int count) {
             if (count <= 0)
                 return;
 #pragma unroll
-            for (int v = V0; v < VPL; v++)
+            for (int v = 0; v < VPL; v++)
                 r[v] = ptx::ld_stream_128(from + (min(lane_vec + v * WPT * 32, count - 1) - lane_vec));
         };
-        using FromVector0  = std::integral_constant<int, 0>;
-        using FromVectorVS = std::integral_constant<int, VS>;
         auto scatter_batch = [&](uint8_t* tile, int count) {
 #pragma unroll
             for (int v = 0; v < VPL; v++)
                 scatter_vector(tile, r[v], lane_vec + v * WPT * 32 < count);
-        };
-        // The first VS * WPT * 32 vectors of a tile come through the team's staging buffer.
-        const uint32_t stage        = w_base + s_own * kStageBytes;
-        int            pending_tile = -1;  // last tile this team asked the copy engine for (chunk-local), if any
-        // asks for the words of chunk-local tile `tile` (vectors off0 .. off1) into the team's buffer
-        auto fetch_words = [&](int tile, int off0, int off1) {
-            pending_tile = tile;
-            if (h == 0 && lane == 0) {
-                const uint32_t bytes = static_cast<uint32_t>(max(min(off1 - off0, VS * WPT * 32), 0)) * 16u;
-                if (bytes > 0) {
-                    ptx::mbar_arrive_expect_tx(words_full(s_own), bytes);
-                    ptx::bulk_copy_g2s(stage, p.words + off0, bytes, words_full(s_own));
-                }
-                else
-                    ptx::mbar_arrive(words_full(s_own));
-            }
-        };
-        // Staging buffer -> registers.  Every lane reads all of its VPL vectors, whether the tile has
-        // that many or not (the buffer always does; what lies beyond the tile's words is stale and is
-        // never scattered): loads without a branch around them pipeline, 2.8 against 11 cycles each.
-        auto take_words = [&]() {
-            uint32_t seen = 0;
-#pragma unroll
-            for (int v = 0; v < VS; v++) {
-                r[v] = ptx::ld_shared_128(stage + static_cast<uint32_t>(lane_vec + v * WPT * 32) * 16u);
-                seen ^= r[v].w;
-            }
-            // a use of every loaded register: the loads have returned before the buffer is handed
-            // back to the copy engine
-            asm volatile("" ::"r"(seen) : "memory");
         };
         const uint4* src = p.words + lane_vec;  // always offset by this lane's first vector
         // Offsets are read two tiles ahead (next*: tile l + D, after*: tile l + 2D) so that the words of
@@ -403,9 +364,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             const int off1 = __ldg(p.tile_offsets + tile_begin + s_own + 1);
             nvec           = off1 - off0;
             src            = p.words + off0 + lane_vec;
-            if (WTMA)
-                fetch_words(s_own, off0, off1);
-            load_words(src, nvec, FromVectorVS{});
+            load_words(src, nvec);
             if (s_own + D < num_tiles) {
                 next0 = __ldg(p.tile_offsets + tile_begin + s_own + D);
                 next1 = __ldg(p.tile_offsets + tile_begin + s_own + D + 1);
@@ -426,24 +385,6 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             uint8_t* const a_tile   = smem_generic + slot * kATileBytes;
             if (use > 0)
                 prefetch_tile(pf0, pf1);  // tile l + kPrefetchRounds * D; its offsets were read one iteration ago
-            if (WTMA) {
-                // this tile's words: staging buffer -> registers, then the buffer takes the team's next tile
-                if (!ptx::mbar_wait_bounded(words_full(s_own), use & 1, abort_word)) {
-                    if (WPT > 1)
-                        asm volatile("bar.arrive %0, %1;" ::"r"(s_own + 1), "n"(WPT * 32) : "memory");
-                    break;
-                }
-                pending_tile = -1;
-                take_words();
-                // The copy engine's next write into the staging buffer must not overtake these reads:
-                // they are generic-proxy accesses that may still be queued in the load/store unit when
-                // the bulk copy is issued, so each reader fences before the team barrier (without the
-                // fence two-warp teams gave wrong results on the GPU).
-                ptx::fence_proxy_async_smem();
-                team_sync();
-                if (has_next)
-                    fetch_words(l + D, next0, next1);
-            }
             if (lap > 0) {
                 if (!ptx::mbar_wait_bounded(tile_free(slot), (lap - 1) & 1, abort_word)) {
                     // A team mate that saw the barrier complete may be waiting at the team barrier below.
@@ -462,13 +403,13 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             // register batches; the tile was requested into L2 two rounds ago, so these loads are short.
 #pragma unroll 1
             for (int done = kBatch; done < nvec; done += kBatch) {
-                load_words(src + done, nvec - done, FromVector0{});
+                load_words(src + done, nvec - done);
                 scatter_batch(a_tile, nvec - done);
             }
             if (has_next) {
                 nvec = next1 - next0;
                 src  = p.words + next0 + lane_vec;
-                load_words(src, nvec, FromVectorVS{});  // the next tile's directly loaded vectors: in flight from here
+                load_words(src, nvec);  // the next tile's words: in flight from here
                 next0 = after0;
                 next1 = after1;
                 if (l + 3 * D < num_tiles) {
@@ -496,8 +437,6 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         }
         if (BM == 0)
             ptx::cp_async_wait_all();
-        if (WTMA && pending_tile >= 0)  // only on the way out of an abandoned block
-            ptx::mbar_wait_quiet(words_full(s_own), (pending_tile / D) & 1, 1000000ull);
     }
     else if (warp >= kFirstMmaWarp) {
         // ------------------------------------------------------------ MMA issue
@@ -599,6 +538,28 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         const int row_in_tile = warp * 32 + lane;
         int       seg         = 0;
         ptx::grid_dependency_wait();
+        // Sum over ranks folded into this epilogue: finished rows go to this rank's partial buffer of the
+        // call's parity, C is written by the sum further down.
+        const bool peer_sum = !TM && p.peer.world > 0;
+        uint32_t   epoch    = 0;
+        half*      c_out    = p.C;
+        if (peer_sum) {
+            uint32_t previous;
+            asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.peer.state) : "memory");
+            epoch = previous + 1;  // every earlier launch on this state has completed (stream order)
+            c_out = p.peer.partial[epoch & 1][p.peer.rank];
+        }
+        // tells every rank that this quarter (warp) of row of tiles `row_tile` is complete in c_out
+        auto announce_rows = [&](int row_tile) {
+            __threadfence_system();
+            __syncwarp();
+            if (lane < p.peer.world)
+                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
+                                 p.peer.flags[lane] + (static_cast<size_t>(row_tile) * kEpilogueWarps + warp) * p.peer.world
+                                 + p.peer.rank),
+                             "r"(epoch)
+                             : "memory");
+        };
 #pragma unroll 1
         for (int l = 0; l < num_tiles; ++seg) {
             const int  t0       = tile_begin + l;
@@ -641,7 +602,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         dst[static_cast<size_t>(c * CH + n) * p.m] = __float2half_rn(v[n]);
                     return;
                 }
-                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
+                uint4* dst = reinterpret_cast<uint4*>(c_out + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
                                                       + static_cast<size_t>(blockIdx.y) * N + c * CH);
                 float w[CH];
 #pragma unroll
@@ -682,6 +643,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     load_chunk(c, v);
                     store_c_chunk(c, v);
                 }
+                if (peer_sum)
+                    announce_rows(row_tile);
             }
             else {
                 // Park the partial row, count arrivals, let the last arriver sum in owner order.
@@ -745,6 +708,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         }
                         store_c_chunk(c, sum);
                     }
+                    if (peer_sum)
+                        announce_rows(row_tile);
                 }
             }
             // only now may the MMA warps overwrite this accumulator set
@@ -755,6 +720,60 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 ptx::mbar_arrive(acc_free(seg & 1));
             l += len;
         }
+        if (peer_sum && blockIdx.y == 0) {
+            // Own tiles done: take rows of tiles in turn, wait for every rank's quarter, add in rank order.
+            const int      tiles_m = p.m / kTileRows;
+            const half* const* parts = p.peer.partial[epoch & 1];
+#pragma unroll 1
+            for (int rt = cta; rt < tiles_m && *abort_word == 0; rt += gridDim.x) {
+                if (lane < p.peer.world) {
+                    const uint32_t* flag = p.peer.flags[p.peer.rank] + (static_cast<size_t>(rt) * kEpilogueWarps + warp) * p.peer.world + lane;
+                    const uint64_t  start = ptx::global_timer_ns();
+#pragma unroll 1
+                    for (uint32_t polls = 0;; polls++) {
+                        uint32_t seen;
+                        asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(flag) : "memory");
+                        if (static_cast<int32_t>(seen - epoch) >= 0 || *abort_word != 0)
+                            break;
+                        if ((polls & 255u) == 255u && ptx::global_timer_ns() - start > p.peer.limit_ns) {
+                            *abort_word = 1;  // a rank never arrived: give up, the status word reports it
+                            break;
+                        }
+                    }
+                }
+                __syncwarp();
+                if (*abort_word != 0)
+                    break;
+                const size_t row = static_cast<size_t>(rt) * kTileRows + row_in_tile;
+#pragma unroll 1
+                for (int c = 0; c < N / 8; c++) {
+                    // all ranks' loads are issued before the first is used: one NVLink round trip per chunk
+                    uint4 v[kMaxPeers];
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; r++)
+                        if (r < p.peer.world)  // a peer's memory, rewritten every other call: never from a cache
+                            v[r] = __ldcv(reinterpret_cast<const uint4*>(parts[r] + row * N) + c);
+                    float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+                    for (int r = 0; r < kMaxPeers; r++)
+                        if (r < p.peer.world) {
+                            const __half2* hv = reinterpret_cast<const __half2*>(&v[r]);
+#pragma unroll
+                            for (int k = 0; k < 4; k++) {
+                                const float2 f = __half22float2(hv[k]);
+                                sum[2 * k] += f.x;
+                                sum[2 * k + 1] += f.y;
+                            }
+                        }
+                    uint4    o;
+                    __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+                    for (int k = 0; k < 4; k++)
+                        oh[k] = __floats2half2_rn(sum[2 * k], sum[2 * k + 1]);
+                    reinterpret_cast<uint4*>(p.C + row * N)[c] = o;
+                }
+            }
+        }
     }
 
     // ---------------------------------------------------------------- exit
@@ -762,6 +781,17 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     __syncthreads();
     if (threadIdx.x == 0 && *abort_word != 0)
         atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
+    if (threadIdx.x == 0 && p.peer.world > 0) {
+        // the last block to get here advances the epoch for the next launch on this state
+        uint32_t previous;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.peer.state) : "memory");
+        __threadfence();
+        if (atomicAdd(p.peer.state + 1, 1u) == gridDim.x * gridDim.y - 1) {
+            p.peer.state[1] = 0;
+            __threadfence();
+            p.peer.state[0] = previous + 1;
+        }
+    }
     if (warp == kFirstMmaWarp) {
         ptx::tc_fence_after_sync();
         ptx::tmem_dealloc(tmem_base, kTmemCols);

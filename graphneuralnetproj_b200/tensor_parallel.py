@@ -155,3 +155,70 @@ class RowParallelSpMM:
         if self.peer is not None:
             return self.peer.reduce().view(self.M, self.N)
         return all_reduce_partial(self.C, group)
+
+
+class FusedRowParallelSpMM:
+    """One rank's part of a row-parallel layer with the sum over ranks folded into the SpMM kernel
+    (spmm_b200_spmm_row_parallel): one launch per call, no collective library, replayable from a CUDA graph.
+    Holds the symmetric partial buffers (two, used alternately by the kernel), the symmetric flag array and
+    the epoch state.  Every rank must construct it and call `forward` the same number of times.
+    With `group=None` and no process group (or a world of one) it runs stand-alone on one GPU."""
+
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None):
+        import ctypes
+
+        import torch
+        import torch.distributed as dist
+
+        from . import spmm_api
+        self._api = spmm_api
+        self.words, self.offsets = words_dev, offsets_dev
+        self.M, self.N, self.K, self.split_k = M, N, K_shard, split_k
+        dev = words_dev.device
+        distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
+        self.rank = dist.get_rank(group) if distributed else 0
+        self.world = dist.get_world_size(group) if distributed else 1
+        flag_words = (M // TILE_M) * 4 * self.world
+        ptr_array = ctypes.c_void_p * self.world
+        if distributed:
+            import os
+            os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only
+            import torch.distributed._symmetric_memory as symm_mem
+            group = group if group is not None else dist.group.WORLD
+            self.partials = [symm_mem.empty(M * N, dtype=torch.float16, device=dev) for _ in range(2)]
+            self.flags = symm_mem.empty(flag_words, dtype=torch.int32, device=dev)
+            self.flags.zero_()
+            handles = [symm_mem.rendezvous(b, group) for b in self.partials]
+            flag_handle = symm_mem.rendezvous(self.flags, group)
+            self._handles = handles + [flag_handle]  # keep the mappings alive
+            self._partial_ptrs = (ctypes.c_void_p * (2 * self.world))(*[int(p) for h in handles for p in h.buffer_ptrs])
+            self._flag_ptrs = ptr_array(*[int(p) for p in flag_handle.buffer_ptrs])
+        else:
+            self.partials = [torch.empty(M * N, dtype=torch.float16, device=dev) for _ in range(2)]
+            self.flags = torch.zeros(flag_words, dtype=torch.int32, device=dev)
+            self._partial_ptrs = (ctypes.c_void_p * 2)(self.partials[0].data_ptr(), self.partials[1].data_ptr())
+            self._flag_ptrs = ptr_array(self.flags.data_ptr())
+        self.state = torch.zeros(2, dtype=torch.int32, device=dev)
+        self.C = torch.zeros((M, N), dtype=torch.float16, device=dev)
+        self.workspace = torch.zeros(spmm_api.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
+        torch.cuda.synchronize(dev)
+        if distributed:
+            dist.barrier(group)  # nobody signals before every flag array is zero
+
+    def forward(self, B_shard_dev, stream=None, limit_ms=2000, words=None):
+        """`words`: another device copy of the same encoded weights to read this call (benchmarks rotate through
+        copies to keep the weights out of L2); default: the tensor given at construction."""
+        import ctypes
+
+        import torch
+        if stream is None:
+            stream = torch.cuda.current_stream()
+        words = self.words if words is None else words
+        rc = self._api.LIB.spmm_b200_spmm_row_parallel(
+            ctypes.c_void_p(stream.cuda_stream), ctypes.c_void_p(words.data_ptr()), ctypes.c_void_p(self.offsets.data_ptr()),
+            ctypes.c_void_p(B_shard_dev.data_ptr()), ctypes.c_void_p(self.C.data_ptr()), self.M, self.N, self.K,
+            ctypes.c_void_p(self.workspace.data_ptr()), self.split_k, self._partial_ptrs, self._flag_ptrs, self.rank, self.world,
+            ctypes.c_void_p(self.state.data_ptr()), limit_ms)
+        if rc != 0:
+            raise RuntimeError("spmm_b200_spmm_row_parallel failed with cudaError %d" % rc)
+        return self.C

@@ -165,6 +165,42 @@ int spmm_b200_allreduce_partials_replayable(void*              stream,
                                             size_t             count,
                                             void*              state,
                                             unsigned           limit_ms);
+/* spmm_b200_spmm_splitk (unstructured mode, N in {8, 16, 32, 64}) of one rank's K shard of a row-parallel
+ * layer with the sum over the ranks folded into the kernel: no second launch and no collective library
+ * on the critical path.  No counterpart in the reference (single-GPU; FasterTransformer all-reduces
+ * after the product, third_party/ft.patch:2822-2846 is followed by its NCCL call).  Every rank writes
+ * its finished rows into its own partial buffer, flags them to all ranks row of tiles by row of tiles,
+ * and the thread blocks that run out of tiles add the ranks' partial rows in rank order out of the
+ * peers' memory (plain loads over NVLink, no multimem) into C; every rank ends up with the same bits.
+ *   partial_buffers  host array of 2 * world device pointers, [parity * world + rank]: rank's partial
+ *                    result of M * N halves for calls of that epoch parity, mapped into this process
+ *                    (symmetric memory); 16-byte aligned
+ *   flag_arrays      host array of world device pointers: rank r's flag array of (M / 128) * 4 * world
+ *                    32-bit words, zero before the first call, mapped into this process
+ *   state            two 32-bit words of this rank's own device memory, zero before the first call and
+ *                    used by this sequence of calls only (the epoch lives there, so the call can be
+ *                    captured in a CUDA graph and replayed)
+ *   limit_ms         how long a block waits for the other ranks (0 = 2000); when it runs out C is left
+ *                    incomplete and spmm_b200_device_status() reports 1
+ * world 1..8 (1 degenerates to a copy through the partial buffer); every rank must make the matching
+ * call.  One process per GPU; the ranks must not share a GPU (each waits for the others). */
+int spmm_b200_spmm_row_parallel(void*        stream,
+                                const void*  Compressed_A,
+                                const int*   TileOffsets,
+                                const void*  B,
+                                void*        C,
+                                int          M_Global,
+                                int          N_Global,
+                                int          K_Global,
+                                void*        Reduction_Workspace,
+                                int          Split_K,
+                                void* const* partial_buffers,
+                                void* const* flag_arrays,
+                                int          rank,
+                                int          world,
+                                void*        state,
+                                unsigned     limit_ms);
+
 /* 0, or 1 if a wait inside spmm_b200_allreduce_partials ran out (synchronises the device). */
 int spmm_b200_allreduce_status(int reset);
 

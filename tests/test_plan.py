@@ -92,3 +92,20 @@ def test_replayed_reduction_is_exact(sp):
         if arrivals[row] == g_last - g_first + 1:
             result[row] = sum(slots[x + ab] for x in range(g_first, g_last + 1))
     assert np.array_equal(result, contrib.reshape(tiles_m, tiles_k).sum(axis=1))
+
+
+def test_built_in_scratch_holds_every_partition_over_148_sms(sp):
+    """The slot arithmetic behind spmm_b200_spmm_own_scratch's refusal: a partition over 148 thread blocks parks at
+    most 295 partial tiles, 9.7 MB at N = 64, inside the 10 MiB array, so no shape is refused on a B200 for lack of
+    scratch; with the 304 blocks the schedule allows at most (a device with more SMs) some shapes would not fit,
+    which is what the refusal is for."""
+    scratch = 10 << 20
+    slot = 128 * 64 * 4
+    worst = 0
+    for tiles_m, tiles_k in ((72, 144), (216, 144), (288, 144), (72, 576), (56, 112), (1, 4096), (8192, 3), (148, 149), (295, 7)):
+        _, _, used = sp.plan(tiles_m, tiles_k, 148, 1 << 40)
+        worst = max(worst, used)
+        assert used * slot <= scratch, (tiles_m, tiles_k, used)
+    assert worst <= 295
+    _, _, used = sp.plan(1000, 7, 304, 1 << 40)
+    assert used * slot > scratch

@@ -106,6 +106,26 @@ else:
                     for out in outs:
                         assert np.array_equal(out.cpu().numpy().view(np.uint16), total), replay
             assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
+        if mode == "row_fused":
+            # the sum over ranks folded into the SpMM kernel: un-captured calls, then a captured pair replayed
+            fused = tp.FusedRowParallelSpMM(layer.words, layer.offsets, M, N, k)
+            for call in range(3):
+                fused.C.fill_(float("nan"))
+                out = fused.forward(Bd)
+                torch.cuda.synchronize()
+                assert np.array_equal(out.cpu().numpy().view(np.uint16), total), call
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, stream=stream):
+                    fused.forward(Bd)
+                    out = fused.forward(Bd)
+                for replay in range(5):
+                    fused.C.fill_(float("nan"))
+                    g.replay()
+                    torch.cuda.synchronize()
+                    assert np.array_equal(out.cpu().numpy().view(np.uint16), total), replay
+            assert sp.device_status() == 0
     else:
         part = torch.from_numpy(oracle.spmm_from_csl(w, o, Bs, M, k).view(np.float16).astype(np.float32))
         total = tp.all_reduce_partial(part).numpy().astype(np.float16).view(np.uint16)
@@ -138,7 +158,7 @@ def test_two_gloo_ranks_on_cpu(mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["column", "row", "row_peer", "row_peer_graph"])
+@pytest.mark.parametrize("mode", ["column", "row", "row_peer", "row_peer_graph", "row_fused"])
 def test_two_nccl_ranks_on_gpus(mode):
     import torch
     if torch.cuda.device_count() < 2:
