@@ -152,8 +152,8 @@ class Layer:
             dense_copies = max(1, int(np.ceil(ROTATE_BYTES / (2.0 * m * k))))
             d0 = torch.from_numpy(A.view(np.float16)).to(dev)
             self.dense = [d0] + [d0.clone() for _ in range(dense_copies - 1)]
-        self.peer = None      # two PeerAllReduce objects used alternately (row-parallel layers, world > 1)
-        self.fused = None     # FusedRowParallelSpMM: the sum over ranks inside the SpMM kernel
+        self.pair = None      # row-parallel layers, world > 1: fp32 partial rows + the reduction kernel over peer memory
+        self.fused = None     # the same sum inside the SpMM kernel
         self.result = self.C  # where the layer's final result lies after a step
 
     def launch(self, sp, copy, C=None):
@@ -220,6 +220,20 @@ def run_ours(args):
             dist.barrier()
         torch.cuda.synchronize()
 
+    def leave(code):
+        """Ends the process once every rank is done, without tearing down the process group, the captured graphs and
+        the symmetric-memory mappings one by one (with several ranks that teardown was seen to hang)."""
+        sys.stdout.flush()
+        sys.stderr.flush()
+        if world > 1:
+            try:
+                torch.cuda.synchronize()
+                dist.barrier()
+            except Exception:
+                pass
+            os._exit(code)
+        raise SystemExit(code)
+
     def reduce_max(values):
         t = torch.tensor(values, dtype=torch.float64, device=dev)
         if world > 1:
@@ -244,8 +258,8 @@ def run_ours(args):
     def add_peer_reducers(some_layers):
         for L in some_layers:
             if L.split == "cols":
-                L.peer = [tp.PeerAllReduce(L.M * N, dev, replayable=True) for _ in range(2)]
-                L.fused = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k)
+                L.pair = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=False)
+                L.fused = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=True)
 
     layers = build(LAYERS, 0, True)
     # ---- the sum over ranks of the layers split by K: NCCL all-reduce, and the library's own kernel
@@ -258,19 +272,17 @@ def run_ours(args):
             if rank == 0:
                 print("peer-memory reduction unavailable:", exc, file=sys.stderr)
         peer_ok = reduce_sum([1.0 if peer_ok else 0.0])[0] == world
-    # "fused": sum over ranks inside the SpMM kernel; "peer": a second kernel over peer memory; "nccl": all-reduce
-    modes = ["none"] if world == 1 else (["fused", "peer", "nccl", "none"] if peer_ok else ["nccl", "none"])
+    # "peer": fp32 partial rows, then the library's reduction kernel over peer memory (two launches); "fused": the same
+    # sum inside the SpMM kernel (one launch); "nccl": fp16 results all-reduced by NCCL; "none": no sum (timing only)
+    modes = ["none"] if world == 1 else (["peer", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
     main_mode = modes[0]
 
     def run_layer(L, copy, mode, use):
         """SpMM of layer L (+ the sum over ranks for a layer split by K).  `use`: running count of uses of L, for the
         alternation between its two peer-reduction objects."""
-        if L.split == "cols" and mode == "fused":
-            L.result = L.fused.forward(L.B, words=L.words[copy % len(L.words)]).view(torch.int16)
-        elif L.split == "cols" and mode == "peer":
-            red = L.peer[use & 1]
-            L.launch(sp, copy, red.next_buffer().view(torch.int16).view(L.M, N))
-            L.result = red.reduce().view(torch.int16).view(L.M, N)
+        if L.split == "cols" and mode in ("fused", "peer"):
+            layer = L.fused if mode == "fused" else L.pair
+            L.result = layer.forward(L.B, words=L.words[copy % len(L.words)]).view(torch.int16)
         else:
             L.launch(sp, copy)
             if L.split == "cols" and mode == "nccl":
@@ -310,7 +322,7 @@ def run_ours(args):
         entry["roofline_frac"] = round(L.algo_bytes / entry["spmm_us"] / 1e3 / hbm_peak, 4)
         entry["hbm_floor_us"] = round(L.algo_bytes / hbm_peak / 1e3, 2)
         if L.split == "cols" and world > 1:
-            best = min(entry["spmm_plus_%s_reduce_us" % mode] for mode in modes[:-1])
+            best = entry["spmm_plus_%s_reduce_us" % modes[0]]
             entry["limited_by"] = ("sum over ranks: +%.1f us on a %.1f us product (HBM floor %.1f us)"
                                    % (best - entry["spmm_us"], entry["spmm_us"], entry["hbm_floor_us"]))
         else:
@@ -451,14 +463,13 @@ def run_ours(args):
         raise RuntimeError("a wait inside the peer-memory reduction ran out")
     weight_bytes, algo_bytes = reduce_sum([sum(L.weight_bytes for L in layers), sum(L.algo_bytes for L in layers)])
     if rank != 0:
-        if world > 1:
-            dist.destroy_process_group()
-        return
+        leave(0)
     value = weight_bytes / (ms_per_step * 1e-3) / 1e9
     achieved = algo_bytes / world / (ms_per_step * 1e-3) / 1e9  # per GPU: the roofline is a per-GPU figure
     launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode == "peer" else 0)
-    reduce_note = {"none": "no collective (one GPU)", "fused": "inside the SpMM kernel, plain NVLink peer loads",
-                   "peer": "library kernel over peer memory (plain NVLink peer loads)", "nccl": "NCCL all-reduce"}[main_mode]
+    reduce_note = {"none": "no collective (one GPU)", "fused": "fp32 partials summed inside the SpMM kernel, plain NVLink peer loads",
+                   "peer": "fp32 partials summed by the library's reduction kernel, plain NVLink peer loads",
+                   "nccl": "NCCL all-reduce of fp16 results"}[main_mode]
     line = {
         "metric": METRIC,
         "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
@@ -507,10 +518,7 @@ def run_ours(args):
     if not verified:
         line["error"] = "verification against the fp64 oracle failed"
     print(json.dumps(line), flush=True)
-    if world > 1:
-        dist.destroy_process_group()
-    if not verified:
-        raise SystemExit(1)
+    leave(0 if verified else 1)
 
 
 def prefill_point(sp, torch, dev, M, K, N, p):

@@ -34,7 +34,8 @@ __device__ int g_device_status_allreduce;  // 1 after a wait for the peers ran o
 constexpr int kMaxRanks = 16;
 
 struct AllReduceParams {
-    const uint4* partial[kMaxRanks];  // every rank's partial result, count halves each
+    const uint4* partial[kMaxRanks];  // every rank's partial result, count halves (or floats) each
+    const uint4* partial_odd[kMaxRanks];  // fp32 form: the buffers used by calls of odd epoch (partial: even)
     uint32_t*    flags[kMaxRanks];    // flags[p] = rank p's flag array (world entries, one per sender)
     uint4*       out;                 // local result
     size_t       vectors;             // count / 8
@@ -44,6 +45,9 @@ struct AllReduceParams {
     unsigned long long limit_ns;
 };
 
+// F32: the partial results are fp32 (two 16-byte vectors per eight outputs) and lie in the buffer set of the
+// call's epoch parity; they are rounded to fp16 once, after the sum.
+template<bool F32>
 __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_constant__ AllReduceParams p)
 {
     __shared__ int ok;
@@ -79,17 +83,37 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
         }
     }
     __syncthreads();
+    const uint4* const* partial = (F32 && (epoch & 1u)) ? p.partial_odd : p.partial;
     for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; ok && i < p.vectors;
          i += static_cast<size_t>(gridDim.x) * blockDim.x) {
         float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-        for (int r = 0; r < p.world; r++) {
-            const uint4    v = __ldcv(p.partial[r] + i);  // peer memory, rewritten every other call: never from a cache
-            const __half2* h = reinterpret_cast<const __half2*>(&v);
+        if (F32) {
+            // all ranks' loads first, then the sums in rank order: one NVLink round trip per eight outputs
+            float4 v[kMaxRanks][2];
 #pragma unroll
-            for (int k = 0; k < 4; k++) {
-                const float2 f = __half22float2(h[k]);
-                sum[2 * k] += f.x;
-                sum[2 * k + 1] += f.y;
+            for (int r = 0; r < kMaxRanks; r++)
+                if (r < p.world) {
+                    const float4* src = reinterpret_cast<const float4*>(partial[r]) + 2 * i;
+                    v[r][0]           = __ldcv(src);
+                    v[r][1]           = __ldcv(src + 1);
+                }
+#pragma unroll
+            for (int r = 0; r < kMaxRanks; r++)
+                if (r < p.world) {
+                    sum[0] += v[r][0].x, sum[1] += v[r][0].y, sum[2] += v[r][0].z, sum[3] += v[r][0].w;
+                    sum[4] += v[r][1].x, sum[5] += v[r][1].y, sum[6] += v[r][1].z, sum[7] += v[r][1].w;
+                }
+        }
+        else {
+            for (int r = 0; r < p.world; r++) {
+                const uint4    v = __ldcv(partial[r] + i);  // peer memory, rewritten every other call: never from a cache
+                const __half2* h = reinterpret_cast<const __half2*>(&v);
+#pragma unroll
+                for (int k = 0; k < 4; k++) {
+                    const float2 f = __half22float2(h[k]);
+                    sum[2 * k] += f.x;
+                    sum[2 * k + 1] += f.y;
+                }
             }
         }
         uint4    o;
@@ -118,17 +142,23 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
 namespace spmm_b200 {
 namespace {
 int launch_allreduce(void* stream, const void* const* partial_buffers, void* const* flag_arrays, int rank, int world, void* out,
-                     size_t count, uint32_t epoch, uint32_t* state, unsigned limit_ms)
+                     size_t count, uint32_t epoch, uint32_t* state, unsigned limit_ms, bool f32 = false)
 {
     if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || count % 8 != 0 || !out || !partial_buffers
-        || !flag_arrays || (epoch == 0 && state == nullptr))
+        || !flag_arrays || (epoch == 0 && state == nullptr) || (f32 && state == nullptr))
         return static_cast<int>(cudaErrorInvalidValue);
     AllReduceParams p;
     for (int r = 0; r < world; r++) {
         if (!partial_buffers[r] || !flag_arrays[r] || (reinterpret_cast<uintptr_t>(partial_buffers[r]) & 15u))
             return static_cast<int>(cudaErrorInvalidValue);
-        p.partial[r] = static_cast<const uint4*>(partial_buffers[r]);
-        p.flags[r]   = static_cast<uint32_t*>(flag_arrays[r]);
+        p.partial[r]     = static_cast<const uint4*>(partial_buffers[r]);
+        p.partial_odd[r] = p.partial[r];
+        if (f32) {  // two buffer sets, parity-major: [parity * world + rank]
+            if (!partial_buffers[world + r] || (reinterpret_cast<uintptr_t>(partial_buffers[world + r]) & 15u))
+                return static_cast<int>(cudaErrorInvalidValue);
+            p.partial_odd[r] = static_cast<const uint4*>(partial_buffers[world + r]);
+        }
+        p.flags[r] = static_cast<uint32_t*>(flag_arrays[r]);
     }
     if (reinterpret_cast<uintptr_t>(out) & 15u)
         return static_cast<int>(cudaErrorInvalidValue);
@@ -149,7 +179,8 @@ int launch_allreduce(void* stream, const void* const* partial_buffers, void* con
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs                                       = attr;
     config.numAttrs                                    = 1;
-    cudaError_t e = cudaLaunchKernelEx(&config, allreduce_partials_kernel, p);
+    cudaError_t e = f32 ? cudaLaunchKernelEx(&config, allreduce_partials_kernel<true>, p)
+                        : cudaLaunchKernelEx(&config, allreduce_partials_kernel<false>, p);
     return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }
 }  // namespace
@@ -198,4 +229,20 @@ extern "C" int spmm_b200_allreduce_status(int reset)
         cudaMemcpyToSymbol(spmm_b200::g_device_status_allreduce, &zero, sizeof(int));
     }
     return status;
+}
+
+extern "C" int spmm_b200_allreduce_partials_f32(void*              stream,
+                                                const void* const* partial_buffers,
+                                                void* const*       flag_arrays,
+                                                int                rank,
+                                                int                world,
+                                                void*              out,
+                                                size_t             count,
+                                                void*              state,
+                                                unsigned           limit_ms)
+{
+    if (state == nullptr || (reinterpret_cast<uintptr_t>(state) & 3u))
+        return static_cast<int>(cudaErrorInvalidValue);
+    return spmm_b200::launch_allreduce(stream, partial_buffers, flag_arrays, rank, world, out, count, 0,
+                                       static_cast<uint32_t*>(state), limit_ms, true);
 }

@@ -771,7 +771,8 @@ int spmm_b200_spmm_row_parallel(void*        stream,
                                 int          rank,
                                 int          world,
                                 void*        state,
-                                unsigned     limit_ms)
+                                unsigned     limit_ms,
+                                int          partial_only)
 {
     using namespace spmm_b200;
     if (world < 1 || world > kMaxPeers || rank < 0 || rank >= world || !partial_buffers || !flag_arrays || !state
@@ -787,7 +788,7 @@ int spmm_b200_spmm_row_parallel(void*        stream,
             void* buffer = partial_buffers[parity * world + r];
             if (!buffer || (reinterpret_cast<uintptr_t>(buffer) & 15u))
                 return static_cast<int>(cudaErrorInvalidValue);
-            peer.partial[parity][r] = static_cast<half*>(buffer);
+            peer.partial[parity][r] = static_cast<float*>(buffer);
         }
         if (!flag_arrays[r] || (reinterpret_cast<uintptr_t>(flag_arrays[r]) & 3u))
             return static_cast<int>(cudaErrorInvalidValue);
@@ -796,6 +797,7 @@ int spmm_b200_spmm_row_parallel(void*        stream,
     peer.state    = static_cast<uint32_t*>(state);
     peer.rank     = rank;
     peer.world    = world;
+    peer.partial_only = partial_only ? 1 : 0;
     peer.limit_ns = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
     return static_cast<int>(spmm_tiled_csl(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A), TileOffsets,
                                            static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global, K_Global,

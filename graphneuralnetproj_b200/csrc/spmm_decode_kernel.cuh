@@ -75,17 +75,22 @@ constexpr int kMaxPeers = 8;  // ranks of a row-parallel (split by K) layer whos
 
 // Sum over the ranks of a layer split by K, folded into the SpMM's epilogue (no counterpart in the
 // reference, which is single-GPU; its FasterTransformer glue all-reduces with NCCL after the product).
-// Every rank writes its finished rows to its own partial buffer instead of C, tells every peer row of
-// tiles by row of tiles (one flag per quarter of a row of tiles and sender, carrying the call's epoch),
-// and once a block has finished its own tiles it takes rows of tiles in turn, waits for all ranks'
-// flags and adds the ranks' partial rows in rank order out of the peers' memory (plain loads over
-// NVLink).  Epochs only grow, so nothing is reset; the partial buffers alternate with the epoch's
-// parity, so a fast rank's next product never overwrites what a slow peer is still reading.
+// Every rank writes its finished rows, still in fp32, to its own partial buffer instead of C, tells every
+// peer row of tiles by row of tiles (one flag per quarter of a row of tiles and sender, carrying the
+// call's epoch), and once a block has finished its own tiles it takes rows of tiles in turn, waits for
+// all ranks' flags, adds the ranks' partial rows in rank order out of the peers' memory (plain loads
+// over NVLink) and rounds once to fp16.  Epochs only grow, so nothing is reset; the partial buffers
+// alternate with the epoch's parity, so a fast rank's next product never overwrites what a slow peer is
+// still reading.  fp32 partials because fp16 ones put the mean relative error of the sum right at the
+// 1e-3 acceptance gate (entries much smaller than their partial sums).
 struct PeerSumParams {
-    half*     partial[2][kMaxPeers] = {};  // [epoch parity][rank]: that rank's partial result [M][N], mapped here
+    float*    partial[2][kMaxPeers] = {};  // [epoch parity][rank]: that rank's partial result, fp32 [M][N], mapped here
     uint32_t* flags[kMaxPeers]      = {};  // flags[r]: rank r's flag array, (M / 128) * 4 * world words
     uint32_t* state                 = nullptr;  // this rank's: [0] epoch of the previous call, [1] blocks finished
     int       rank = 0, world = 0;              // world == 0: no sum over ranks
+    // 1: only write this rank's fp32 partial rows (buffer of parity (state[0] + 1) & 1); the flags, the sum and
+    // the advance of the epoch are left to the reduction kernel launched next in the stream
+    int       partial_only = 0;
     unsigned long long limit_ns = 0;
 };
 
@@ -542,19 +547,23 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         // call's parity, C is written by the sum further down.
         const bool peer_sum = !TM && p.peer.world > 0;
         uint32_t   epoch    = 0;
-        half*      c_out    = p.C;
+        float*     c32_out  = nullptr;
         if (peer_sum) {
             uint32_t previous;
             asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.peer.state) : "memory");
-            epoch = previous + 1;  // every earlier launch on this state has completed (stream order)
-            c_out = p.peer.partial[epoch & 1][p.peer.rank];
+            epoch   = previous + 1;  // every earlier launch on this state has completed (stream order)
+            c32_out = p.peer.partial[epoch & 1][p.peer.rank];
         }
-        // tells every rank that this quarter (warp) of row of tiles `row_tile` is complete in c_out
+        // Tells every rank that this quarter (warp) of row of tiles `row_tile` is complete in c32_out.  One
+        // system-scope fence per warp, by one lane, after the warp's stores have been ordered before it by the
+        // warp barrier: a fence in every lane made the announcement take about 16 us at the end of a launch.
         auto announce_rows = [&](int row_tile) {
-            __threadfence_system();
+            __syncwarp();
+            if (lane == 0)
+                asm volatile("fence.acq_rel.sys;" ::: "memory");
             __syncwarp();
             if (lane < p.peer.world)
-                asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(
                                  p.peer.flags[lane] + (static_cast<size_t>(row_tile) * kEpilogueWarps + warp) * p.peer.world
                                  + p.peer.rank),
                              "r"(epoch)
@@ -602,7 +611,16 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         dst[static_cast<size_t>(c * CH + n) * p.m] = __float2half_rn(v[n]);
                     return;
                 }
-                uint4* dst = reinterpret_cast<uint4*>(c_out + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
+                if (peer_sum) {
+                    // this rank's share of the sum over ranks stays in fp32 (N <= 64, one column block)
+                    float4* dst32 = reinterpret_cast<float4*>(c32_out + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * N
+                                                              + c * CH);
+#pragma unroll
+                    for (int i = 0; i < CH / 4; i++)
+                        dst32[i] = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                    return;
+                }
+                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
                                                       + static_cast<size_t>(blockIdx.y) * N + c * CH);
                 float w[CH];
 #pragma unroll
@@ -643,7 +661,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     load_chunk(c, v);
                     store_c_chunk(c, v);
                 }
-                if (peer_sum)
+                if (peer_sum && !p.peer.partial_only)
                     announce_rows(row_tile);
             }
             else {
@@ -708,7 +726,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         }
                         store_c_chunk(c, sum);
                     }
-                    if (peer_sum)
+                    if (peer_sum && !p.peer.partial_only)
                         announce_rows(row_tile);
                 }
             }
@@ -720,10 +738,10 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 ptx::mbar_arrive(acc_free(seg & 1));
             l += len;
         }
-        if (peer_sum && blockIdx.y == 0) {
+        if (peer_sum && !p.peer.partial_only && blockIdx.y == 0) {
             // Own tiles done: take rows of tiles in turn, wait for every rank's quarter, add in rank order.
             const int      tiles_m = p.m / kTileRows;
-            const half* const* parts = p.peer.partial[epoch & 1];
+            float* const* parts = p.peer.partial[epoch & 1];
 #pragma unroll 1
             for (int rt = cta; rt < tiles_m && *abort_word == 0; rt += gridDim.x) {
                 if (lane < p.peer.world) {
@@ -747,23 +765,22 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                 const size_t row = static_cast<size_t>(rt) * kTileRows + row_in_tile;
 #pragma unroll 1
                 for (int c = 0; c < N / 8; c++) {
-                    // all ranks' loads are issued before the first is used: one NVLink round trip per chunk
-                    uint4 v[kMaxPeers];
+                    // eight columns at a time; all ranks' loads are issued before the first is used, so a chunk
+                    // costs one NVLink round trip
+                    float4 v[kMaxPeers][2];
 #pragma unroll
                     for (int r = 0; r < kMaxPeers; r++)
-                        if (r < p.peer.world)  // a peer's memory, rewritten every other call: never from a cache
-                            v[r] = __ldcv(reinterpret_cast<const uint4*>(parts[r] + row * N) + c);
+                        if (r < p.peer.world) {  // a peer's memory, rewritten every other call: never from a cache
+                            const float4* src = reinterpret_cast<const float4*>(parts[r] + row * N) + 2 * c;
+                            v[r][0] = __ldcv(src);
+                            v[r][1] = __ldcv(src + 1);
+                        }
                     float sum[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
 #pragma unroll
                     for (int r = 0; r < kMaxPeers; r++)
                         if (r < p.peer.world) {
-                            const __half2* hv = reinterpret_cast<const __half2*>(&v[r]);
-#pragma unroll
-                            for (int k = 0; k < 4; k++) {
-                                const float2 f = __half22float2(hv[k]);
-                                sum[2 * k] += f.x;
-                                sum[2 * k + 1] += f.y;
-                            }
+                            sum[0] += v[r][0].x, sum[1] += v[r][0].y, sum[2] += v[r][0].z, sum[3] += v[r][0].w;
+                            sum[4] += v[r][1].x, sum[5] += v[r][1].y, sum[6] += v[r][1].z, sum[7] += v[r][1].w;
                         }
                     uint4    o;
                     __half2* oh = reinterpret_cast<__half2*>(&o);
@@ -781,7 +798,7 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
     __syncthreads();
     if (threadIdx.x == 0 && *abort_word != 0)
         atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
-    if (threadIdx.x == 0 && p.peer.world > 0) {
+    if (threadIdx.x == 0 && p.peer.world > 0 && !p.peer.partial_only) {
         // the last block to get here advances the epoch for the next launch on this state
         uint32_t previous;
         asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.peer.state) : "memory");

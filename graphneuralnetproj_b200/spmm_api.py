@@ -70,8 +70,12 @@ def _load():
     lib.spmm_b200_allreduce_partials_replayable.restype = ctypes.c_int
     lib.spmm_b200_spmm_row_parallel.argtypes = [ctypes.c_void_p] * 5 + [ctypes.c_int] * 3 + [ctypes.c_void_p, ctypes.c_int] + \
         [ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int, ctypes.c_void_p,
-         ctypes.c_uint]
+         ctypes.c_uint, ctypes.c_int]
     lib.spmm_b200_spmm_row_parallel.restype = ctypes.c_int
+    lib.spmm_b200_allreduce_partials_f32.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                                     ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int,
+                                                     ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_uint]
+    lib.spmm_b200_allreduce_partials_f32.restype = ctypes.c_int
     lib.spmm_b200_allreduce_status.argtypes = [ctypes.c_int]
     lib.spmm_b200_allreduce_status.restype = ctypes.c_int
     lib.spmm_b200_set_weights_constant.argtypes = [ctypes.c_int]

@@ -158,13 +158,15 @@ class RowParallelSpMM:
 
 
 class FusedRowParallelSpMM:
-    """One rank's part of a row-parallel layer with the sum over ranks folded into the SpMM kernel
-    (spmm_b200_spmm_row_parallel): one launch per call, no collective library, replayable from a CUDA graph.
-    Holds the symmetric partial buffers (two, used alternately by the kernel), the symmetric flag array and
-    the epoch state.  Every rank must construct it and call `forward` the same number of times.
-    With `group=None` and no process group (or a world of one) it runs stand-alone on one GPU."""
+    """One rank's part of a row-parallel layer with fp32 partial results summed over the ranks out of peer
+    memory (spmm_b200_spmm_row_parallel): no collective library, one rounding, replayable from a CUDA graph.
+    `fused=True`: the sum is folded into the SpMM kernel (one launch per call); `fused=False`: the SpMM only
+    writes its fp32 partial rows and spmm_b200_allreduce_partials_f32 follows as a second launch (the faster
+    form on B200: see include/spmm_b200.h).  Holds the symmetric partial buffers (two, used alternately), the
+    symmetric flag array and the epoch state.  Every rank must construct it and call `forward` the same number
+    of times.  With no process group (or a world of one) it runs stand-alone on one GPU."""
 
-    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None):
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None, fused=True):
         import ctypes
 
         import torch
@@ -174,6 +176,7 @@ class FusedRowParallelSpMM:
         self._api = spmm_api
         self.words, self.offsets = words_dev, offsets_dev
         self.M, self.N, self.K, self.split_k = M, N, K_shard, split_k
+        self.fused = fused
         dev = words_dev.device
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.rank = dist.get_rank(group) if distributed else 0
@@ -185,7 +188,7 @@ class FusedRowParallelSpMM:
             os.environ.setdefault("TORCH_SYMM_MEM_DISABLE_MULTICAST", "1")  # plain peer mappings only
             import torch.distributed._symmetric_memory as symm_mem
             group = group if group is not None else dist.group.WORLD
-            self.partials = [symm_mem.empty(M * N, dtype=torch.float16, device=dev) for _ in range(2)]
+            self.partials = [symm_mem.empty(M * N, dtype=torch.float32, device=dev) for _ in range(2)]
             self.flags = symm_mem.empty(flag_words, dtype=torch.int32, device=dev)
             self.flags.zero_()
             handles = [symm_mem.rendezvous(b, group) for b in self.partials]
@@ -194,7 +197,7 @@ class FusedRowParallelSpMM:
             self._partial_ptrs = (ctypes.c_void_p * (2 * self.world))(*[int(p) for h in handles for p in h.buffer_ptrs])
             self._flag_ptrs = ptr_array(*[int(p) for p in flag_handle.buffer_ptrs])
         else:
-            self.partials = [torch.empty(M * N, dtype=torch.float16, device=dev) for _ in range(2)]
+            self.partials = [torch.empty(M * N, dtype=torch.float32, device=dev) for _ in range(2)]
             self.flags = torch.zeros(flag_words, dtype=torch.int32, device=dev)
             self._partial_ptrs = (ctypes.c_void_p * 2)(self.partials[0].data_ptr(), self.partials[1].data_ptr())
             self._flag_ptrs = ptr_array(self.flags.data_ptr())
@@ -218,7 +221,13 @@ class FusedRowParallelSpMM:
             ctypes.c_void_p(stream.cuda_stream), ctypes.c_void_p(words.data_ptr()), ctypes.c_void_p(self.offsets.data_ptr()),
             ctypes.c_void_p(B_shard_dev.data_ptr()), ctypes.c_void_p(self.C.data_ptr()), self.M, self.N, self.K,
             ctypes.c_void_p(self.workspace.data_ptr()), self.split_k, self._partial_ptrs, self._flag_ptrs, self.rank, self.world,
-            ctypes.c_void_p(self.state.data_ptr()), limit_ms)
+            ctypes.c_void_p(self.state.data_ptr()), limit_ms, 0 if self.fused else 1)
         if rc != 0:
             raise RuntimeError("spmm_b200_spmm_row_parallel failed with cudaError %d" % rc)
+        if not self.fused:
+            rc = self._api.LIB.spmm_b200_allreduce_partials_f32(
+                ctypes.c_void_p(stream.cuda_stream), self._partial_ptrs, self._flag_ptrs, self.rank, self.world,
+                ctypes.c_void_p(self.C.data_ptr()), self.M * self.N, ctypes.c_void_p(self.state.data_ptr()), limit_ms)
+            if rc != 0:
+                raise RuntimeError("spmm_b200_allreduce_partials_f32 failed with cudaError %d" % rc)
         return self.C

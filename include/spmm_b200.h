@@ -182,6 +182,12 @@ int spmm_b200_allreduce_partials_replayable(void*              stream,
  *                    captured in a CUDA graph and replayed)
  *   limit_ms         how long a block waits for the other ranks (0 = 2000); when it runs out C is left
  *                    incomplete and spmm_b200_device_status() reports 1
+ *   partial_only     0: as described.  1: the kernel only writes this rank's fp32 partial rows (into the
+ *                    buffer of the coming epoch's parity) and neither flags, sums nor advances the epoch:
+ *                    spmm_b200_allreduce_partials_f32 on the same buffers, flag arrays and state, launched
+ *                    next in the stream, does that (C is then not written by this call).  Measured on two
+ *                    to eight B200s the two-launch form is the faster one: a system-scope fence at the
+ *                    end of a kernel that keeps the memory system busy costs more than a launch.
  * world 1..8 (1 degenerates to a copy through the partial buffer); every rank must make the matching
  * call.  One process per GPU; the ranks must not share a GPU (each waits for the others). */
 int spmm_b200_spmm_row_parallel(void*        stream,
@@ -199,7 +205,23 @@ int spmm_b200_spmm_row_parallel(void*        stream,
                                 int          rank,
                                 int          world,
                                 void*        state,
-                                unsigned     limit_ms);
+                                unsigned     limit_ms,
+                                int          partial_only);
+
+/* The sum over ranks for spmm_b200_spmm_row_parallel(..., partial_only = 1): the replayable reduction
+ * above on fp32 partial results, rounded to fp16 once.  partial_buffers: the same 2 * world pointers
+ * (M * N floats each, [parity * world + rank]); flag_arrays: world pointers to at least `world` words
+ * each; state: the two words shared with the SpMM calls (this kernel advances the epoch); out: count
+ * halves. */
+int spmm_b200_allreduce_partials_f32(void*              stream,
+                                     const void* const* partial_buffers,
+                                     void* const*       flag_arrays,
+                                     int                rank,
+                                     int                world,
+                                     void*              out,
+                                     size_t             count,
+                                     void*              state,
+                                     unsigned           limit_ms);
 
 /* 0, or 1 if a wait inside spmm_b200_allreduce_partials ran out (synchronises the device). */
 int spmm_b200_allreduce_status(int reset);

@@ -324,9 +324,11 @@ def test_weights_written_by_the_preceding_kernel(sp, oracle, torch_cuda):
 
 
 def test_row_parallel_entry_point_on_one_rank(sp, torch_cuda):
-    """spmm_b200_spmm_row_parallel with a world of one: the finished rows travel through the partial buffer, the
-    flags are this rank's own, and the sum over 'ranks' is a copy.  Same bits as SpMM_SplitK_API, call after call
-    (the epoch advances and the partial buffers alternate), also when replayed from a CUDA graph."""
+    """spmm_b200_spmm_row_parallel with a world of one, in both forms (the sum inside the SpMM kernel, or the SpMM
+    writing fp32 partial rows and spmm_b200_allreduce_partials_f32 following it): the finished rows travel through
+    the partial buffer in fp32, the flags are this rank's own, and the sum over 'ranks' is a copy with one rounding.
+    Same bits as SpMM_SplitK_API, call after call (the epoch advances and the partial buffers alternate), also when
+    replayed from a CUDA graph."""
     torch = torch_cuda
     from graphneuralnetproj_b200 import tensor_parallel as tp
     dev = torch.device("cuda:0")
@@ -335,23 +337,26 @@ def test_row_parallel_entry_point_on_one_rank(sp, torch_cuda):
         B = sp.synth_fp16((K, N), 800 + N, 1.0, 0.0)
         words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
         want = run_spmm(sp, torch, words, offsets, B, M, N, K, 8)
-        layer = tp.FusedRowParallelSpMM(torch.from_numpy(words.view(np.int32)).to(dev), torch.from_numpy(offsets).to(dev), M, N, K)
+        wd = torch.from_numpy(words.view(np.int32)).to(dev)
+        od = torch.from_numpy(offsets).to(dev)
         Bd = torch.from_numpy(B.view(np.int16)).to(dev)
-        for call in range(3):
-            layer.C.fill_(float("nan"))
-            out = layer.forward(Bd)
-            torch.cuda.synchronize()
-            assert sp.device_status() == 0
-            assert np.array_equal(out.cpu().numpy().view(np.uint16), want), (M, K, N, call)
-        stream = torch.cuda.Stream()
-        with torch.cuda.stream(stream):
-            graph = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(graph, stream=stream):
-                out = layer.forward(Bd)
-            for replay in range(4):
+        for fused in (True, False):
+            layer = tp.FusedRowParallelSpMM(wd, od, M, N, K, fused=fused)
+            for call in range(3):
                 layer.C.fill_(float("nan"))
-                graph.replay()
+                out = layer.forward(Bd)
                 torch.cuda.synchronize()
-                assert np.array_equal(out.cpu().numpy().view(np.uint16), want), (M, K, N, "replay", replay)
-        assert int(layer.state[0].item()) == 3 + 4 and int(layer.state[1].item()) == 0
-        assert sp.device_status() == 0
+                assert sp.device_status() == 0
+                assert np.array_equal(out.cpu().numpy().view(np.uint16), want), (M, K, N, fused, call)
+            stream = torch.cuda.Stream()
+            with torch.cuda.stream(stream):
+                graph = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(graph, stream=stream):
+                    out = layer.forward(Bd)
+                for replay in range(4):
+                    layer.C.fill_(float("nan"))
+                    graph.replay()
+                    torch.cuda.synchronize()
+                    assert np.array_equal(out.cpu().numpy().view(np.uint16), want), (M, K, N, fused, "replay", replay)
+            assert int(layer.state[0].item()) == 3 + 4 and int(layer.state[1].item()) == 0
+            assert sp.device_status() == 0 and sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
