@@ -135,7 +135,7 @@ class Layer:
         words, offsets, n_offsets = sp.InitSparseMatrixA_API(A, m, N, k)
         self.weight_bytes = 4 * words.size + 4 * n_offsets
         self.algo_bytes = algorithmic_bytes(words.size, n_offsets, m, k, N)
-        copies = max(1, int(np.ceil(ROTATE_BYTES / self.weight_bytes)))
+        copies = min(12, max(1, int(np.ceil(ROTATE_BYTES / self.weight_bytes))))
         first = torch.from_numpy(words.view(np.int32)).to(dev)
         self.words = [first] + [first.clone() for _ in range(copies - 1)]
         self.offsets = torch.from_numpy(offsets).to(dev)
@@ -149,7 +149,7 @@ class Layer:
         self.ws = torch.zeros(sp.workspace_bytes(m, N, split_k) // 2, dtype=torch.int16, device=dev)
         self.dense = None
         if keep_dense:
-            dense_copies = max(1, int(np.ceil(ROTATE_BYTES / (2.0 * m * k))))
+            dense_copies = min(12, max(1, int(np.ceil(ROTATE_BYTES / (2.0 * m * k)))))
             d0 = torch.from_numpy(A.view(np.float16)).to(dev)
             self.dense = [d0] + [d0.clone() for _ in range(dense_copies - 1)]
         self.pair = None      # row-parallel layers, world > 1: fp32 partial rows + the reduction kernel over peer memory
@@ -202,6 +202,8 @@ def run_ours(args):
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    if world > 1:  # the ranks share the host: each gets its share of the cores for generating and encoding its shards
+        os.environ.setdefault("SPMM_B200_THREADS", str(max(1, (os.cpu_count() or 8) // world)))
     if not torch.cuda.is_available():
         raise SystemExit("bench.py needs a CUDA device; there is no CPU fallback")
     torch.cuda.set_device(local)

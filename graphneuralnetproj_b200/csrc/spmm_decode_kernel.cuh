@@ -704,23 +704,40 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
 #pragma unroll
                         for (int n = 0; n < CH; n++)
                             sum[n] = 0.0f;
+                        // the other owners' slots, four at a time: their loads are issued together (one L2
+                        // round trip per group instead of one per owner), the sums follow in owner order
 #pragma unroll 1
-                        for (int g = g_first; g <= g_last; g++) {
-                            if (g == cta) {
+                        for (int g0 = g_first; g0 <= g_last; g0 += 4) {
+                            float4 theirs[4][CH / 4];
 #pragma unroll
-                                for (int n = 0; n < CH; n++)
-                                    sum[n] += own[n];
+                            for (int u = 0; u < 4; u++) {
+                                const int g = g0 + u;
+                                if (g <= g_last && g != cta) {
+                                    const float4* slot_row = reinterpret_cast<const float4*>(
+                                        slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N + c * CH);
+#pragma unroll
+                                    for (int i = 0; i < CH / 4; i++)
+                                        theirs[u][i] = __ldcg(slot_row + i);
+                                }
                             }
-                            else {
-                                const float4* theirs = reinterpret_cast<const float4*>(
-                                    slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N + c * CH);
 #pragma unroll
-                                for (int i = 0; i < CH / 4; i++) {
-                                    const float4 x = __ldcg(theirs + i);
-                                    sum[4 * i] += x.x;
-                                    sum[4 * i + 1] += x.y;
-                                    sum[4 * i + 2] += x.z;
-                                    sum[4 * i + 3] += x.w;
+                            for (int u = 0; u < 4; u++) {
+                                const int g = g0 + u;
+                                if (g > g_last)
+                                    break;
+                                if (g == cta) {
+#pragma unroll
+                                    for (int n = 0; n < CH; n++)
+                                        sum[n] += own[n];
+                                }
+                                else {
+#pragma unroll
+                                    for (int i = 0; i < CH / 4; i++) {
+                                        sum[4 * i] += theirs[u][i].x;
+                                        sum[4 * i + 1] += theirs[u][i].y;
+                                        sum[4 * i + 2] += theirs[u][i].z;
+                                        sum[4 * i + 3] += theirs[u][i].w;
+                                    }
                                 }
                             }
                         }

@@ -220,7 +220,7 @@ def spmm_f64_threads(A, B, threads=None):
     import threading
     A = _as_u16(A)
     M = A.shape[0]
-    threads = max(1, min(threads or (os.cpu_count() or 1), 32, M))
+    threads = max(1, min(threads or int(os.environ.get("SPMM_B200_THREADS", 0)) or (os.cpu_count() or 1), 32, M))
     out = np.empty((M, B.shape[1]), np.float64)
     bounds = [M * t // threads for t in range(threads + 1)]
 
