@@ -179,6 +179,21 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tenso
                  : "memory");
 }
 
+// The same load issued by either block of a pair (a cluster of two): the box lands in the issuing block's
+// shared memory, the bytes are counted on an mbarrier of either block (`bar_cluster`: address in the
+// cluster's shared window, see map_to_cta), which is how the partner's half of an operand is reported to
+// the block that issues the pair's MMAs.  No multicast: every block fetches what it stages itself.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar_cluster)
+{
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
+                     dst_smem),
+                 "l"(tensor_map),
+                 "r"(x),
+                 "r"(y),
+                 "r"(bar_cluster)
+                 : "memory");
+}
+
 // Asks the memory system to bring `bytes` (a multiple of 16, from a 16-byte aligned address) into L2.
 __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes)
 {
@@ -317,6 +332,111 @@ __device__ __forceinline__ void tmem_cp_128x128b(uint32_t taddr, uint64_t smem_d
 __device__ __forceinline__ void umma_commit(uint32_t bar)
 {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---------------------------------------------------------------- pairs of SMs (a cluster of two blocks)
+// tcgen05 with .cta_group::2: one thread of the even block of the pair issues MMAs that use the tensor
+// cores, shared memory and TMEM of both blocks (M = 256: each block holds 128 rows of A and of the
+// accumulator, and half of the columns of B).
+__device__ __forceinline__ uint32_t cluster_cta_rank()
+{
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// The address, in the cluster's shared window, of the same shared-memory location in block `rank`.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr_cta, uint32_t rank)
+{
+    uint32_t out;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(out) : "r"(smem_addr_cta), "r"(rank));
+    return out;
+}
+
+// Arrives on an mbarrier anywhere in the cluster (address from map_to_cta); what this thread observed
+// or wrote before is visible to a cluster-scope acquire of the completed phase.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar_cluster)
+{
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar_cluster) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint32_t bar, uint32_t parity, uint32_t suspend_ns)
+{
+    uint32_t done;
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2, %3;\n\t"
+                 "selp.b32 %0, 1, 0, p;\n\t}"
+                 : "=r"(done)
+                 : "r"(bar), "r"(parity), "r"(suspend_ns)
+                 : "memory");
+    return done != 0;
+}
+
+// mbar_wait_bounded for a barrier of this block that the other block of the pair arrives on.
+__device__ __forceinline__ bool
+mbar_wait_bounded_cluster(uint32_t bar, uint32_t parity, volatile int* abort_word, uint64_t limit_ns = kWaitLimitNs)
+{
+    uint64_t start = 0;
+#pragma unroll 1
+    for (uint32_t polls = 0;; polls++) {
+        if (mbar_try_wait_cluster(bar, parity, polls < SPMM_B200_PLAIN_POLLS ? 0u : kSuspendNs))
+            return true;
+        if (*abort_word != 0)
+            return false;
+        if ((polls & 255u) == 255u) {
+            const uint64_t now = global_timer_ns();
+            if (start == 0)
+                start = now;
+            else if (now - start > limit_ns) {
+                *abort_word = 1;
+                return false;
+            }
+        }
+    }
+}
+
+// Barrier over all threads of the cluster (both blocks): every thread arrives, every thread waits.
+__device__ __forceinline__ void cluster_sync_all()
+{
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t result_smem, uint32_t columns)
+{
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(result_smem), "r"(columns)
+                 : "memory");
+}
+
+__device__ __forceinline__ void tmem_relinquish_pair()
+{
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t columns)
+{
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(columns) : "memory");
+}
+
+// D[tmem of both blocks] (+)= A[shared memory of both blocks] * B[shared memory of both blocks]: the
+// descriptors give the offsets of each block's part, the same in both blocks.
+__device__ __forceinline__ void
+umma_f16_ss_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate)
+{
+    asm volatile("{\n\t.reg .pred p;\n\t"
+                 "setp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}" ::"r"(d_tmem),
+                 "l"(a_desc),
+                 "l"(b_desc),
+                 "r"(idesc),
+                 "r"(accumulate)
+                 : "memory");
+}
+
+// Arrives on an mbarrier of either block of the pair (address in the cluster's shared window) once
+// every pair MMA issued so far by this thread has completed.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar_cluster)
+{
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar_cluster) : "memory");
 }
 
 __device__ __forceinline__ void tmem_ld_wait()

@@ -12,6 +12,7 @@
 #include "../../include/spmm_b200.h"
 #include "host_threads.h"
 #include "spmm_decode_kernel.cuh"
+#include "spmm_pair_kernel.cuh"
 #include "spmm_structured_kernel.cuh"
 
 namespace spmm_b200 {
@@ -39,6 +40,7 @@ struct DecodeConfig {
 struct DeviceInfo {
     int  sm_count = 0;
     bool attrs_set[16] = {};  // cudaFuncSetAttribute done, per kernel instantiation
+    int  pair_clusters[2] = {};  // clusters of the pair kernel the device holds at once, per NM
 };
 
 std::mutex g_device_lock;  // guards DeviceInfo, the workspace -> counter set table and the caches below
@@ -142,6 +144,83 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
     attr[0].val.programmaticStreamSerializationAllowed = 1;
     config.attrs                                       = attr;
     config.numAttrs                                    = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kern, params);
+    return e != cudaSuccess ? e : cudaGetLastError();
+}
+
+
+// Widths that are multiples of 256 (prefill) run on pairs of SMs where the shape allows (see
+// spmm_pair_kernel.cuh); spmm_b200_set_pair_kernel(0) keeps them on the single-block kernel.
+std::atomic<int> g_pair_kernel{1};
+
+#ifndef PAIR_SA2
+#define PAIR_SA2 8
+#define PAIR_SB2 3
+#define PAIR_SA1 8
+#define PAIR_SB1 5
+#endif
+template<int NM>
+struct PairConfig {
+    static constexpr int SA = NM == 2 ? PAIR_SA2 : PAIR_SA1;
+    static constexpr int SB = NM == 2 ? PAIR_SB2 : PAIR_SB1;
+    static constexpr int D = SA, VPL = 14;
+};
+
+// How many clusters of two blocks of the pair kernel the device holds at once (0: cannot run it).
+template<int NM>
+int pair_clusters(DeviceInfo& dev, int n_index)
+{
+    using Cfg          = PairConfig<NM>;
+    constexpr int smem = pair_smem_bytes<NM, Cfg::SA, Cfg::SB>();
+    static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
+    auto kern = spmm_pair_kernel<NM, Cfg::D, Cfg::VPL, Cfg::SA, Cfg::SB>;
+    std::lock_guard<std::mutex> guard(g_device_lock);
+    if (!dev.attrs_set[n_index]) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return 0;
+        }
+        cudaLaunchConfig_t config = {};
+        config.gridDim            = dim3(2 * (dev.sm_count / 2));
+        config.blockDim           = dim3(pair_threads<Cfg::D>());
+        config.dynamicSmemBytes   = smem;
+        cudaLaunchAttribute attr[1];
+        attr[0].id               = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = 2;
+        attr[0].val.clusterDim.y = 1;
+        attr[0].val.clusterDim.z = 1;
+        config.attrs             = attr;
+        config.numAttrs          = 1;
+        int clusters             = 0;
+        if (cudaOccupancyMaxActiveClusters(&clusters, kern, &config) != cudaSuccess) {
+            (void)cudaGetLastError();
+            clusters = 0;
+        }
+        dev.pair_clusters[NM - 1] = std::min(clusters, dev.sm_count / 2);
+        dev.attrs_set[n_index]    = true;
+    }
+    return dev.pair_clusters[NM - 1];
+}
+
+template<int NM>
+cudaError_t launch_pair(cudaStream_t stream, const DecodeParams& params, int column_blocks)
+{
+    using Cfg                 = PairConfig<NM>;
+    auto kern                 = spmm_pair_kernel<NM, Cfg::D, Cfg::VPL, Cfg::SA, Cfg::SB>;
+    cudaLaunchConfig_t config = {};
+    config.gridDim            = dim3(2 * params.sched.num_ctas, column_blocks);
+    config.blockDim           = dim3(pair_threads<Cfg::D>());
+    config.dynamicSmemBytes   = pair_smem_bytes<NM, Cfg::SA, Cfg::SB>();
+    config.stream             = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id                                         = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x                           = 2;
+    attr[0].val.clusterDim.y                           = 1;
+    attr[0].val.clusterDim.z                           = 1;
+    attr[1].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                       = attr;
+    config.numAttrs                                    = 2;
     cudaError_t e = cudaLaunchKernelEx(&config, kern, params);
     return e != cudaSuccess ? e : cudaGetLastError();
 }
@@ -255,11 +334,7 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
         return cudaErrorUnknown;
     }
-    // the widest slice that divides N: the sparse tiles are decoded once per column block
-    const int n_block       = !wide ? N_Global : (N_Global % 256 == 0 ? 256 : (N_Global % 128 == 0 ? 128 : 64));
-    const int column_blocks = N_Global / n_block;
-    if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kTileCols != 0
-        || static_cast<long>(M_Global / kTileRows) * column_blocks > kMaxRowTiles || Split_K < 1)
+    if (M_Global <= 0 || K_Global <= 0 || M_Global % kTileRows != 0 || K_Global % kTileCols != 0 || Split_K < 1)
         return cudaErrorInvalidValue;
     if (!Compressed_A || !TileOffsets || !B || !C || !aligned16(Compressed_A) || !aligned16(B)
         || !aligned16(Reduction_Workspace) || (!token_major && !aligned16(C)))
@@ -270,6 +345,23 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     if (e != cudaSuccess)
         return e;
     DeviceInfo& dev = device_info(device);
+
+    // Multiples of 256 columns on 256-row multiples: pairs of SMs, 512 columns per restored tile where N allows.
+    int pair_nm = 0, clusters = 0;
+    if (wide && N_Global % 256 == 0 && M_Global % (2 * kTileRows) == 0 && addend == nullptr && peer == nullptr
+        && g_pair_kernel.load(std::memory_order_relaxed) != 0) {
+        pair_nm  = N_Global % 512 == 0 ? 2 : 1;
+        clusters = pair_nm == 2 ? pair_clusters<2>(dev, 15) : pair_clusters<1>(dev, 14);
+        if (clusters == 0)
+            pair_nm = 0;
+    }
+    // the widest slice that divides N: the sparse tiles are decoded once per column block
+    const int n_block       = !wide ? N_Global
+                                    : (pair_nm ? pair_nm * kPairColsPerMma
+                                               : (N_Global % 256 == 0 ? 256 : (N_Global % 128 == 0 ? 128 : 64)));
+    const int column_blocks = N_Global / n_block;
+    if (static_cast<long>(M_Global / kTileRows) * column_blocks > kMaxRowTiles)
+        return cudaErrorInvalidValue;
 
     const int  tiles_m = M_Global / kTileRows, tiles_k = K_Global / kTileCols;
     // every column block gets an equal share of the workspace for its partial tiles
@@ -315,6 +407,16 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     params.tiles_k      = tiles_k;
     params.m            = M_Global;
     params.ld           = N_Global;
+    if (pair_nm != 0) {
+        // the schedule is over rows of tile pairs and clusters; each of a cluster's two blocks parks its own rows
+        cached_schedule(PlanKey{tiles_m / 2, tiles_k, std::max(1, clusters / std::min(column_blocks, 4)), slots_granted / 2},
+                        params.sched);
+        params.slots_per_block_column = 2 * params.sched.slots_used;
+        e = describe_b(params.b_map, B, N_Global, K_Global, n_block);
+        if (e != cudaSuccess)
+            return e;
+        return pair_nm == 2 ? launch_pair<2>(stream, params, column_blocks) : launch_pair<1>(stream, params, column_blocks);
+    }
     // with several column blocks the blocks of one column share the SMs with the other columns
     cached_schedule(PlanKey{tiles_m, tiles_k, wide ? std::max(1, dev.sm_count / std::min(column_blocks, 4)) : dev.sm_count,
                             slots_granted},
@@ -819,6 +921,22 @@ int spmm_b200_spmm_splitk_token_major(void*       stream,
                                             static_cast<const uint4*>(Compressed_A), TileOffsets,
                                             static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global,
                                             K_Global, static_cast<half*>(Reduction_Workspace), Split_K));
+}
+
+#ifdef SPMM_PAIR_TIMING
+extern "C" int spmm_b200_pair_timing(unsigned long long* out)
+{
+    return static_cast<int>(cudaMemcpyFromSymbol(out, spmm_b200::g_pair_timing, sizeof(unsigned long long) * 512 * 24));
+}
+extern "C" int spmm_b200_pair_events(unsigned long long* out)
+{
+    return static_cast<int>(cudaMemcpyFromSymbol(out, spmm_b200::g_pair_events, sizeof(unsigned long long) * 2 * 160 * 8));
+}
+#endif
+
+int spmm_b200_set_pair_kernel(int enabled)
+{
+    return spmm_b200::g_pair_kernel.exchange(enabled ? 1 : 0);
 }
 
 int spmm_b200_set_weights_constant(int constant)

@@ -1,0 +1,505 @@
+// Prefill-size "load-as-sparse, compute-as-dense" SpMM on pairs of SMs: C[M][N] = A * B for N a multiple
+// of 256 (beyond the reference's N <= 64, csrc/SpMM_API.cu:105-196), A in tiled-CSL.
+//
+// At these widths the single-block kernel (spmm_decode_kernel.cuh) is bound by shared-memory bandwidth
+// -- per restored tile and 256 columns the decoders spend about 450 wavefronts and the tensor core
+// reads 128 (A) + 256 (B) -- and by the B slices it pulls out of L2 (32 KB per tile and 256 columns).
+// Here two blocks on neighbouring SMs (a cluster of two) work on 256 rows together with
+// tcgen05.mma.cta_group::2, M = 256:
+//   - each block restores the tiles of its own 128 rows (rows 256 * pr + 128 * rank ...) into its own
+//     shared memory, exactly as the single-block kernel does;
+//   - each block stages only half of the columns of a B slice (128 of every 256); the pair MMA reads
+//     both halves, so the B traffic per block out of L2 and out of shared memory halves;
+//   - with NM = 2 a restored tile serves 512 columns (two MMAs of 256 columns per k step), so it is
+//     decoded once per 512 columns instead of once per 256.  The accumulators then fill the 512 TMEM
+//     columns and the epilogue of a row no longer overlaps the next row (about 2 % at K = 12288).
+// Per block and restored tile at NM = 2: 450 (decode) + 2 * (128 + 128) (operands) = 962 wavefronts for
+// 1024 cycles of MMA, against 450 + 384 = 834 for 512 cycles in the single-block kernel.
+//
+// Roles per block: warps 0..3 epilogue; warp 4 allocates TMEM and, in the even block (the leader),
+// issues the pair MMAs; warp 5 issues the tiled TMA loads of the block's half of the B slices, buffer
+// by buffer as they come free; warps 6.. are D decoder warps.  Synchronisation across the pair: the
+// "ready" barrier of a tile lives in the leader; the partner's decoder arrives on it at cluster scope and
+// the partner's TMA loads count their bytes on it (cp.async.bulk.tensor with .cta_group::2), so the MMA
+// lane waits once per tile (a lane in the partner that forwarded its block's readiness was measured to
+// take 0.6 us per tile, more than the MMAs of a tile); the leader's tcgen05.commit arrives on the
+// "done" / acc_full barriers of both blocks (one commit per block, the second through the cluster-window
+// address of the partner's barrier); the partner's epilogue warps arrive on the leader's acc_free barrier.  Every wait is bounded; a block that gives up still
+// reaches the cluster barrier at the end, so its partner never waits for it without limit.
+#pragma once
+
+#include "spmm_decode_kernel.cuh"
+
+namespace spmm_b200 {
+
+#ifdef SPMM_PAIR_TIMING
+__device__ unsigned long long g_pair_timing[512][24];
+__device__ unsigned long long g_pair_events[2][160][8];
+#define PAIR_EV(l, e) do { if (blockIdx.x < 2 && blockIdx.y == 0 && (l) < 160) g_pair_events[blockIdx.x][l][e] = ptx::global_timer_ns(); } while (0)
+#define PAIR_ACC(i, expr) do { const unsigned long long t_ = ptx::global_timer_ns(); expr; acc_[i] += ptx::global_timer_ns() - t_; } while (0)
+#define PAIR_ACC_DECL unsigned long long acc_[6] = {0, 0, 0, 0, 0, 0}
+#define PAIR_ACC_STORE(base, n, cond) do { if (cond) for (int i_ = 0; i_ < n; i_++) g_pair_timing[blockIdx.x + gridDim.x * blockIdx.y][base + i_] = acc_[i_]; } while (0)
+#define PAIR_T(i) do { if (warp == 0 && lane == 0) g_pair_timing[blockIdx.x + gridDim.x * blockIdx.y][i] = ptx::global_timer_ns(); } while (0)
+#else
+#define PAIR_T(i) do { } while (0)
+#define PAIR_EV(l, e) do { } while (0)
+#define PAIR_ACC(i, expr) do { expr; } while (0)
+#define PAIR_ACC_DECL
+#define PAIR_ACC_STORE(base, n, cond)
+#endif
+constexpr int kPairColsPerMma = 256;  // columns of one pair MMA; each block stages half of them
+
+// SA buffers for restored tiles of A, SB buffers for this block's half of a B slice (NM * 16 KB each)
+template<int NM, int SA, int SB>
+constexpr int pair_smem_bytes()
+{
+    return 1024 + SA * kATileBytes + SB * NM * BTile<kPairColsPerMma / 2>::kBytes + 512;
+}
+
+template<int D>
+constexpr int pair_threads()
+{
+    return (kFirstMmaWarp + 2 + D) * 32;
+}
+
+// NM  : pair MMAs per k step = 256-column blocks served by one restored tile (1 or 2); the cluster
+//       handles NM * 256 columns (blockIdx.y selects which)
+// D   : decoder warps (tile l of the chunk is restored by warp l % D into A buffer l % SA), each holding
+//       VPL 4-word vectors per lane -- the decode-size kernel's arrangement: eight independent warps keep
+//       enough loads in flight, four teams of two warps were measured 3 x slower per tile
+// SA, SB: ring of A buffers and, separately, of B buffers (tile l uses B buffer l % SB): the B halves are
+//       NM times larger than a restored tile, so fewer of them fit
+//       p.sched partitions (M / 256) rows of tile pairs x (K / 64) among the clusters;
+//       p.slots_per_block_column counts slots of 128 x (NM * 256) floats, two per schedule slot.
+template<int NM, int D, int VPL, int SA, int SB>
+__global__ void __launch_bounds__(pair_threads<D>(), 1)
+spmm_pair_kernel(const __grid_constant__ DecodeParams p)
+{
+    constexpr int NBLK = NM * kPairColsPerMma;  // columns per cluster
+    constexpr int ACC  = 2 / NM;                // accumulator sets of NBLK columns in the 512 TMEM columns
+    using BT           = BTile<kPairColsPerMma / 2>;  // this block's half of a 64 x 256 slice: two 64-column atoms
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t smem_base = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    const uint32_t a_base    = smem_base;
+    const uint32_t b_base    = a_base + SA * kATileBytes;
+    const uint32_t bar_base  = b_base + SB * NM * BT::kBytes;
+    // barriers (8 bytes each): per A buffer "ready" -- the tile of that buffer is restored and its B half has landed
+    // (in the leader also: the partner's are) -- and "free" (the pair MMAs that read the buffer, and the B buffer of
+    // the same tile, have completed); then accumulators full x2, free x2 (leader's).  One wait and two commits per
+    // tile for the MMA lane: its time per tile, not the tensor core's, bounded an earlier form with more barriers.
+    // Both kinds form a ring of R = max(SA, SB) entries indexed by the tile (l % R): the decoder of tile l waits
+    // for the MMAs of tile l - SA (its A buffer), the loader for those of tile l - SB (its B buffer).
+    constexpr int R = SA > SB ? SA : SB;
+    auto ready    = [&](int s) { return bar_base + 8u * s; };
+    auto done     = [&](int s) { return bar_base + 8u * (R + s); };
+    auto acc_full = [&](int b) { return bar_base + 8u * (2 * R + b); };
+    auto acc_free = [&](int b) { return bar_base + 8u * (2 * R + 2 + b); };
+    const uint32_t tmem_slot_addr = bar_base + 8u * (2 * R + 4);
+    uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
+    volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
+    volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
+    static_assert(8 * (2 * R + 4) + 8 <= 512, "barrier block");
+    static_assert(SA >= D, "every decoder warp needs a buffer of its own to start with");
+    static_assert(NM == 1 || NM == 2, "one or two 256-column MMAs per k step");
+
+    const int      warp    = threadIdx.x >> 5;
+    const int      lane    = threadIdx.x & 31;
+    const uint32_t rank    = ptx::cluster_cta_rank();  // 0: leader (issues the MMAs), 1: its partner
+    const int      cluster = blockIdx.x >> 1;
+
+    const int tile_begin = p.sched.chunk_begin[cluster];  // in units of tile pairs: (row of pairs, k tile)
+    const int tile_end   = p.sched.chunk_begin[cluster + 1];
+    const int num_tiles  = tile_end - tile_begin;
+    const int tiles_k    = p.tiles_k;
+    // Tile `l` of the chunk is pair tile t = tile_begin + l = (pr, j); this block's tile of it is tile
+    // (2 pr + rank, j) of the encoded sequence.
+    auto tile_index = [&](int l) {
+        const int t = tile_begin + l;
+        return t + (t / tiles_k + static_cast<int>(rank)) * tiles_k;
+    };
+    constexpr int kLoaderWarp      = kFirstMmaWarp + 1;
+    constexpr int kFirstDecodeWarp = kFirstMmaWarp + 2;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < R; s++) {
+            ptx::mbar_init(ready(s), 3);  // the leader's: both blocks' decoders and the leader's loader (+ both halves' bytes)
+            ptx::mbar_init(done(s), 1);
+        }
+        for (int b = 0; b < 2; b++) {
+            ptx::mbar_init(acc_full(b), 1);
+            ptx::mbar_init(acc_free(b), 2 * kEpilogueWarps);
+        }
+        *abort_word = 0;
+        ptx::mbar_init_fence();
+    }
+    for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(SA * kATileBytes + SB * NM * BT::kBytes); off += blockDim.x * 16u)
+        ptx::st_shared_zero_128(a_base + off);
+    if (warp == kFirstMmaWarp) {
+        ptx::tmem_alloc_pair(tmem_slot_addr, 512);
+        ptx::tmem_relinquish_pair();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::cluster_sync_all();  // both blocks' barriers exist before anyone arrives on the partner's
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    ptx::grid_launch_dependents();
+
+    if (warp >= kFirstDecodeWarp) {
+        // ------------------------------------------------------------ decoder warp (see spmm_decode_kernel)
+        const int      s_own         = warp - kFirstDecodeWarp;  // this warp's first tile and first A buffer
+        const uint32_t leader_ready0 = ptx::map_to_cta(ready(0), 0);
+        uint32_t  slot  = s_own;
+        uint4     r[VPL];
+        int       nvec = 0, next0 = 0, next1 = 0;
+        auto load_words = [&](const uint4* from, int count) {
+            if (count <= 0)
+                return;
+#pragma unroll
+            for (int v = 0; v < VPL; v++)
+                r[v] = ptx::ld_stream_128(from + (min(lane + v * 32, count - 1) - lane));
+        };
+        auto scatter_batch = [&](uint8_t* tile, int count) {
+#pragma unroll
+            for (int v = 0; v < VPL; v++)
+                scatter_vector(tile, r[v], lane + v * 32 < count);
+        };
+        auto request_words = [&](int l) {  // this block's words of chunk tile l into L2, ahead of their turn
+            if (lane == 0 && l < num_tiles) {
+                const int i    = tile_index(l);
+                const int off0 = __ldg(p.tile_offsets + i), off1 = __ldg(p.tile_offsets + i + 1);
+                if (off1 > off0)
+                    ptx::bulk_prefetch_l2(p.words + off0, static_cast<uint32_t>(off1 - off0) * 16u);
+            }
+        };
+        const uint4* src = p.words + lane;
+        if (!p.weights_early)
+            ptx::grid_dependency_wait();
+        if (s_own < num_tiles) {
+            const int i    = tile_index(s_own);
+            const int off0 = __ldg(p.tile_offsets + i), off1 = __ldg(p.tile_offsets + i + 1);
+            nvec           = off1 - off0;
+            src            = p.words + off0 + lane;
+            load_words(src, nvec);
+            if (s_own + D < num_tiles) {
+                const int in = tile_index(s_own + D);
+                next0        = __ldg(p.tile_offsets + in);
+                next1        = __ldg(p.tile_offsets + in + 1);
+            }
+            request_words(s_own + D);
+            request_words(s_own + 2 * D);
+        }
+        ptx::grid_dependency_wait();
+        PAIR_ACC_DECL;
+#pragma unroll 1
+        for (int l = s_own; l < num_tiles; l += D) {
+            const bool     has_next = l + D < num_tiles;
+            const int      before   = l - SA;  // the tile that used this A buffer last
+            uint8_t* const a_tile   = smem_generic + slot * kATileBytes;
+            request_words(l + 3 * D);
+            if (before >= 0) {
+                bool ok_;
+                PAIR_ACC(0, ok_ = ptx::mbar_wait_bounded_cluster(done(before % R), (before / R) & 1, abort_word));
+                if (!ok_)
+                    break;
+                PAIR_ACC(1, {
+#pragma unroll
+                for (int i = 0; i < kATileBytes / (32 * 16); i++)
+                    ptx::st_shared_zero_128(a_base + slot * kATileBytes + lane * 16u + i * 512u);
+                __syncwarp(); });
+            }
+            if (lane == 0) PAIR_EV(l, 0);
+            PAIR_ACC(2, scatter_batch(a_tile, nvec); __syncwarp());
+#pragma unroll 1
+            for (int done = VPL * 32; done < nvec; done += VPL * 32) {
+                load_words(src + done, nvec - done);
+                scatter_batch(a_tile, nvec - done);
+            }
+            if (has_next) {
+                nvec = next1 - next0;
+                src  = p.words + next0 + lane;
+                load_words(src, nvec);
+                if (l + 2 * D < num_tiles) {
+                    const int in = tile_index(l + 2 * D);
+                    next0        = __ldg(p.tile_offsets + in);
+                    next1        = __ldg(p.tile_offsets + in + 1);
+                }
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0) {
+                PAIR_EV(l, 1);
+                if (rank == 0)
+                    ptx::mbar_arrive(ready(l % R));
+                else
+                    ptx::mbar_arrive_cluster(leader_ready0 + 8u * (l % R));
+            }
+            slot += D;
+            if (slot >= SA)
+                slot -= SA;
+        }
+        PAIR_ACC_STORE(8, 3, s_own == 0 && lane == 0);
+    }
+    else if (warp == kLoaderWarp) {
+        // ------------------------------------------------------------ B loader: this block's half of every slice
+        // Columns [rank * 128, rank * 128 + 128) of each of the cluster's 256-column blocks, 64 k rows, as boxes
+        // of 64 columns; a slot's B buffers are refilled as soon as the pair MMAs that read them have completed.
+        ptx::grid_dependency_wait();
+        if (lane == 0) {
+            const uint32_t leader_ready0 = ptx::map_to_cta(ready(0), 0);
+            int j = tile_begin % tiles_k;
+            PAIR_ACC_DECL;
+#pragma unroll 1
+            for (int l = 0; l < num_tiles; l++) {
+                // B buffer l % SB was last read by tile l - SB: wait for that tile's MMAs
+                const int s = l % SB;
+                bool ok_ = true;
+                if (l >= SB)
+                    PAIR_ACC(0, ok_ = ptx::mbar_wait_bounded_cluster(done((l - SB) % R), ((l - SB) / R) & 1, abort_word));
+                if (!ok_)
+                    break;
+                PAIR_EV(l, 2);
+                // the bytes of both halves are counted on the leader's barrier, announced by the leader's loader
+                const uint32_t bar = leader_ready0 + 8u * (l % R);
+                if (rank == 0)
+                    ptx::mbar_arrive_expect_tx(ready(l % R), 2 * NM * BT::kBytes);
+#pragma unroll
+                for (int m = 0; m < NM; m++)
+#pragma unroll
+                    for (int a = 0; a < BT::kAtoms; a++)
+                        ptx::tma_load_2d_pair(b_base + (s * NM + m) * BT::kBytes + a * BT::kAtomBytes, &p.b_map,
+                                         static_cast<int>(blockIdx.y) * NBLK + m * kPairColsPerMma
+                                             + static_cast<int>(rank) * (kPairColsPerMma / 2) + a * BT::kAtomCols,
+                                         j * kTileCols, bar);
+                if (++j == tiles_k)
+                    j = 0;
+            }
+            PAIR_ACC_STORE(16, 1, true);
+        }
+    }
+    else if (warp == kFirstMmaWarp) {
+        ptx::grid_dependency_wait();
+        if (lane == 0 && rank == 0) {
+            // ------------------------------------------------------------ leader: MMA issue for the pair
+            constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(2 * kTileRows, kPairColsPerMma, false, true);
+            const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
+            const uint64_t     b_desc0 = ptx::make_smem_desc(b_base, BT::kLeadingBytes, BT::kGroupBytes, BT::kSwizzleMode);
+            const uint32_t     partner_done0      = ptx::map_to_cta(done(0), 1);
+            const uint32_t     partner_acc_full0  = ptx::map_to_cta(acc_full(0), 1);
+            bool ok  = true;
+            int  seg = 0;
+            PAIR_ACC_DECL;
+#pragma unroll 1
+            for (int l0 = 0; l0 < num_tiles && ok; ++seg) {
+                const int j0  = (tile_begin + l0) % tiles_k;
+                const int len = min(tiles_k - j0, num_tiles - l0);
+                const int set = seg % ACC, use = seg / ACC;
+                const uint32_t d_tmem = tmem_base + set * NBLK;
+                if (use >= 1)
+                    PAIR_ACC(3, ok = ptx::mbar_wait_bounded_cluster(acc_free(set), (use - 1) & 1, abort_word));
+                uint32_t accumulate = 0;
+#pragma unroll 1
+                for (int l = l0; l < l0 + len && ok; l++) {
+                    const int      sa = l % SA, sb = l % SB, e = l % R;
+                    const uint32_t parity = (l / R) & 1;
+                    PAIR_EV(l, 4);
+                    PAIR_ACC(0, ok = ptx::mbar_wait_bounded_cluster(ready(e), parity, abort_word));
+                    PAIR_EV(l, 5);
+                    if (!ok)
+                        break;
+                    ptx::tc_fence_after_sync();
+                    const uint64_t a_desc = a_desc0 + static_cast<uint64_t>(sa * (kATileBytes >> 4));
+#pragma unroll
+                    for (int k = 0; k < kTileCols / 16; k++) {
+#pragma unroll
+                        for (int m = 0; m < NM; m++) {
+                            const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * NM + m) * (BT::kBytes >> 4));
+                            ptx::umma_f16_ss_pair(d_tmem + m * kPairColsPerMma,
+                                                  a_desc + static_cast<uint64_t>((k * 32) >> 4),
+                                                  b_desc + static_cast<uint64_t>((k * 2 * BT::kGroupBytes) >> 4),
+                                                  idesc,
+                                                  k == 0 ? accumulate : 1u);
+                        }
+                    }
+                    ptx::umma_commit_pair(done(e));
+                    ptx::umma_commit_pair(partner_done0 + 8u * e);
+                    PAIR_EV(l, 6);
+                    accumulate = 1;
+                }
+                if (ok) {
+                    ptx::umma_commit_pair(acc_full(set));
+                    ptx::umma_commit_pair(partner_acc_full0 + 8u * set);
+                }
+                l0 += len;
+            }
+            PAIR_ACC_STORE(12, 4, true);
+        }
+    }
+    else {
+        // ------------------------------------------------------------ epilogue: this block's 128 rows x NBLK columns
+        const int      row_in_tile      = warp * 32 + lane;
+        const uint32_t leader_acc_free0 = ptx::map_to_cta(acc_free(0), 0);
+        int            seg              = 0;
+        ptx::grid_dependency_wait();
+        PAIR_T(0);
+        constexpr int CH = 16;
+#pragma unroll 1
+        for (int l = 0; l < num_tiles; ++seg) {
+            const int  t0       = tile_begin + l;
+            const int  pair_row = t0 / tiles_k;
+            const int  row_tile = 2 * pair_row + static_cast<int>(rank);
+            const int  j0       = t0 % tiles_k;
+            const int  len      = min(tiles_k - j0, num_tiles - l);
+            const bool whole    = (j0 == 0) && (len == tiles_k);
+            const int  set = seg % ACC, use = seg / ACC;
+            if (!warp_wait(acc_full(set), use & 1, abort_word, lane))
+                break;
+            ptx::tc_fence_after_sync();
+            PAIR_T(1);
+            auto load_chunk = [&](int c, float* out) {
+                ptx::tmem_ld_x16(tmem_base + set * NBLK + c * CH + (static_cast<uint32_t>(warp * 32) << 16),
+                                 reinterpret_cast<uint32_t*>(out));
+                ptx::tmem_ld_wait();
+            };
+            auto store_c_chunk = [&](int c, const float* v) {
+                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
+                                                      + static_cast<size_t>(blockIdx.y) * NBLK + c * CH);
+#pragma unroll
+                for (int i = 0; i < CH / 8; i++) {
+                    __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]);
+                    __half2 h1 = __floats2half2_rn(v[8 * i + 2], v[8 * i + 3]);
+                    __half2 h2 = __floats2half2_rn(v[8 * i + 4], v[8 * i + 5]);
+                    __half2 h3 = __floats2half2_rn(v[8 * i + 6], v[8 * i + 7]);
+                    uint4   o;
+                    o.x    = *reinterpret_cast<uint32_t*>(&h0);
+                    o.y    = *reinterpret_cast<uint32_t*>(&h1);
+                    o.z    = *reinterpret_cast<uint32_t*>(&h2);
+                    o.w    = *reinterpret_cast<uint32_t*>(&h3);
+                    dst[i] = o;
+                }
+            };
+            if (whole) {
+#pragma unroll 1
+                for (int c = 0; c < NBLK / CH; c++) {
+                    float v[CH];
+                    load_chunk(c, v);
+                    store_c_chunk(c, v);
+                }
+            }
+            else {
+                // A row of pairs whose K range is shared between clusters: park the partial rows, count arrivals
+                // per row of tiles, the last arriver adds the owners' slots in owner order (as in spmm_decode_kernel;
+                // an owner is a cluster, and each of its two blocks has a slot of its own).
+                const int  head_row  = tile_begin / tiles_k;
+                const bool head_part = (tile_begin % tiles_k != 0) || (tile_end < (head_row + 1) * tiles_k);
+                const int  above     = p.sched.split_rows_above[cluster] + ((pair_row != head_row && head_part) ? 1 : 0);
+                int        g_first = cluster, g_last = cluster;
+                while (p.sched.chunk_begin[g_first] > pair_row * tiles_k)
+                    g_first--;
+                while (p.sched.chunk_begin[g_last + 1] < (pair_row + 1) * tiles_k)
+                    g_last++;
+                float* const slots = p.slots + static_cast<size_t>(blockIdx.y) * p.slots_per_block_column * (kTileRows * NBLK);
+                // A slot holds 128 x NBLK floats as [NBLK / 4 groups of four columns][128 rows] float4: the 32 lanes
+                // of a warp (32 rows) write and read 512 contiguous bytes per instruction.  (Row-major slots made
+                // every store 32 partial sectors and the tail of a launch tens of microseconds long.)
+                auto slot_of = [&](int g) {
+                    return reinterpret_cast<float4*>(slots) + (static_cast<size_t>(g + above) * 2 + rank) * (kTileRows * NBLK / 4)
+                           + row_in_tile;
+                };
+                float4* const mine = slot_of(cluster);
+#pragma unroll 1
+                for (int c = 0; c < NBLK / CH; c++) {
+                    float v[CH];
+                    load_chunk(c, v);
+#pragma unroll
+                    for (int i = 0; i < CH / 4; i++)
+                        __stcg(mine + (c * (CH / 4) + i) * kTileRows, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                }
+                PAIR_T(2);
+                __threadfence();
+                __syncwarp();
+                unsigned int  arrived = 0;
+                unsigned int* counter =
+                    &g_row_arrivals[p.counter_set][(blockIdx.y * (p.m / kTileRows) + row_tile) * kEpilogueWarps + warp];
+                if (lane == 0)
+                    arrived = atomicAdd(counter, 1u);
+                arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                PAIR_T(3);
+                if (arrived == static_cast<unsigned int>(g_last - g_first)) {
+                    if (lane == 0)
+                        *counter = 0;
+                    __threadfence();
+#pragma unroll 1
+                    for (int c = 0; c < NBLK / CH; c++) {
+                        float own[CH], sum[CH];
+                        load_chunk(c, own);
+#pragma unroll
+                        for (int n = 0; n < CH; n++)
+                            sum[n] = 0.0f;
+                        // the other owners' slots, four owners at a time: their loads are issued together, the
+                        // sums follow in owner order
+#pragma unroll 1
+                        for (int g0 = g_first; g0 <= g_last; g0 += 4) {
+                            float4 theirs[4][CH / 4];
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int g = g0 + u;
+                                if (g <= g_last && g != cluster) {
+                                    const float4* src = slot_of(g) + c * (CH / 4) * kTileRows;
+#pragma unroll
+                                    for (int i = 0; i < CH / 4; i++)
+                                        theirs[u][i] = __ldcg(src + i * kTileRows);
+                                }
+                            }
+#pragma unroll
+                            for (int u = 0; u < 4; u++) {
+                                const int g = g0 + u;
+                                if (g > g_last)
+                                    break;
+                                if (g == cluster) {
+#pragma unroll
+                                    for (int n = 0; n < CH; n++)
+                                        sum[n] += own[n];
+                                }
+                                else {
+#pragma unroll
+                                    for (int i = 0; i < CH / 4; i++) {
+                                        sum[4 * i] += theirs[u][i].x;
+                                        sum[4 * i + 1] += theirs[u][i].y;
+                                        sum[4 * i + 2] += theirs[u][i].z;
+                                        sum[4 * i + 3] += theirs[u][i].w;
+                                    }
+                                }
+                            }
+                        }
+                        store_c_chunk(c, sum);
+                    }
+                }
+            }
+            PAIR_T(4);
+            // only now may the leader overwrite this accumulator set (in both blocks)
+            ptx::tmem_ld_wait();
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0)
+                ptx::mbar_arrive_cluster(leader_acc_free0 + 8u * set);
+            l += len;
+        }
+    }
+
+    // ---------------------------------------------------------------- exit
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    PAIR_T(5);
+    if (threadIdx.x == 0 && *abort_word != 0)
+        atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
+    // Neither block leaves while its partner may still arrive on its barriers or the leader's MMAs may
+    // still read its shared memory (a block that gave up gets here too).
+    ptx::cluster_sync_all();
+    if (warp == kFirstMmaWarp) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc_pair(tmem_base, 512);
+    }
+}
+
+}  // namespace spmm_b200

@@ -80,6 +80,8 @@ def _load():
     lib.spmm_b200_allreduce_status.restype = ctypes.c_int
     lib.spmm_b200_set_weights_constant.argtypes = [ctypes.c_int]
     lib.spmm_b200_set_weights_constant.restype = ctypes.c_int
+    lib.spmm_b200_set_pair_kernel.argtypes = [ctypes.c_int]
+    lib.spmm_b200_set_pair_kernel.restype = ctypes.c_int
     lib.spmm_b200_workspace_bytes.argtypes = [ctypes.c_int] * 3
     lib.spmm_b200_workspace_bytes.restype = ctypes.c_size_t
     for name in ("spmm_b200_decompose", "spmm_b200_decompose_v1"):
@@ -254,6 +256,11 @@ def set_weights_constant(constant=True):
     """Whether weights may be fetched before the stream predecessor has completed (see include/spmm_b200.h:
     the caller guarantees they are not produced by the kernel just ahead).  Returns the previous setting."""
     return bool(LIB.spmm_b200_set_weights_constant(1 if constant else 0))
+
+
+def set_pair_kernel(enabled=True):
+    """Whether widths that are multiples of 256 run on pairs of SMs (include/spmm_b200.h).  Returns the previous setting."""
+    return bool(LIB.spmm_b200_set_pair_kernel(1 if enabled else 0))
 
 
 def workspace_bytes(M_Global, N_Global, Split_K):

@@ -173,8 +173,8 @@ int spmm_b200_allreduce_partials_replayable(void*              stream,
  * and the thread blocks that run out of tiles add the ranks' partial rows in rank order out of the
  * peers' memory (plain loads over NVLink, no multimem) into C; every rank ends up with the same bits.
  *   partial_buffers  host array of 2 * world device pointers, [parity * world + rank]: rank's partial
- *                    result of M * N halves for calls of that epoch parity, mapped into this process
- *                    (symmetric memory); 16-byte aligned
+ *                    result of M * N floats (fp32, so that the sum is rounded to fp16 once) for calls
+ *                    of that epoch parity, mapped into this process (symmetric memory); 16-byte aligned
  *   flag_arrays      host array of world device pointers: rank r's flag array of (M / 128) * 4 * world
  *                    32-bit words, zero before the first call, mapped into this process
  *   state            two 32-bit words of this rank's own device memory, zero before the first call and
@@ -238,6 +238,15 @@ int spmm_b200_allreduce_status(int reset);
  * Process-wide; returns the previous setting.  No counterpart in the reference, whose launches are
  * fully serialised. */
 int spmm_b200_set_weights_constant(int constant);
+
+/* Widths that are multiples of 256 columns (prefill; beyond the reference's N <= 64) on matrices whose
+ * M is a multiple of 256 run on pairs of SMs (tcgen05.mma.cta_group::2 over a cluster of two blocks:
+ * each block restores the tiles of 128 of the pair's 256 rows and stages half of the columns of a B
+ * slice; with N a multiple of 512 a restored tile serves 512 columns).  0 keeps such calls on the
+ * single-block kernel that serves every other width (for comparison; the results of the two agree
+ * within rounding, not bit for bit, because rows are split between blocks at different k).
+ * Process-wide; returns the previous setting (default 1). */
+int spmm_b200_set_pair_kernel(int enabled);
 
 /* The reference's workspace contract, build/SpMM_API.cuh:34-38:
  * Split_K * M * N * sizeof(half) bytes. */
