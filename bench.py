@@ -532,18 +532,11 @@ def prefill_point(sp, torch, dev, M, K, N, p):
     od = torch.from_numpy(offsets).to(dev)
     Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB300, 1.0).view(np.int16)).to(dev)
     Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
-    ws = torch.zeros(sp.workspace_bytes(M, N, 2) // 2, dtype=torch.int16, device=dev)
-    for _ in range(3):
-        assert sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 2) == 0
-    torch.cuda.synchronize()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    reps = 5
-    e0.record()
-    for _ in range(reps):
-        sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 2)
-    e1.record()
-    torch.cuda.synchronize()
-    us = e0.elapsed_time(e1) * 1000.0 / reps
+    split_k = sp.suggest_split_k(M, K)  # sizes the workspace: room for the partial tiles of a partition over all SMs
+    ws = torch.zeros(sp.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
+    assert sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, split_k) == 0
+    us = time_graph(torch, lambda: sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, split_k))
+    assert sp.device_status() == 0
     return {"M": M, "K": K, "N": N, "sparsity": p, "spmm_us": round(us, 1),
             "dense_equiv_tflops": round(2.0 * M * N * K / us / 1e6, 1),
             "frac_of_tensor_peak": round(2.0 * M * N * K / us / 1e6 / tensor_peak, 4), "tensor_peak_tflops": tensor_peak}
@@ -740,6 +733,29 @@ def run_sweep(args):
     assert sp.device_status() == 0
 
 
+def time_graph(torch, fn, launches=10, replays=3):
+    """Microseconds per call of `fn`, `launches` calls captured in one CUDA graph and replayed (no host time
+    between the kernels), CUDA events on the replaying stream, after warm-up calls and one warm-up replay."""
+    for _ in range(3):
+        fn()
+    torch.cuda.synchronize()
+    stream = torch.cuda.Stream()
+    with torch.cuda.stream(stream):
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph, stream=stream):
+            for _ in range(launches):
+                fn()
+        graph.replay()
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record(stream)
+        for _ in range(replays):
+            graph.replay()
+        e1.record(stream)
+        torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / (launches * replays)
+
+
 def run_prefill(args):
     """Prefill-size points (N >= 256): dense-equivalent TFLOP/s = 2*M*N*K / t against the measured
     dense tensor peak, with cuBLAS dense fp16 beside it.  One JSON line per point."""
@@ -761,23 +777,23 @@ def run_prefill(args):
             for N in [int(x) for x in args.prefill_n.split(",")]:
                 Bd = torch.from_numpy(sp.synth_fp16((K, N), 0xB300, 1.0).view(np.int16)).to(dev)
                 Cd = torch.zeros((M, N), dtype=torch.int16, device=dev)
-                ws = torch.zeros(sp.workspace_bytes(M, N, 2) // 2, dtype=torch.int16, device=dev)
+                # the workspace of the reference's contract for the Split_K the library suggests: room for the fp32
+                # partial tiles of a partition of the rows over all SMs (with less, rows cannot be split and SMs idle)
+                split_k = sp.suggest_split_k(M, K)
+                ws = torch.zeros(sp.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
+                Bh = Bd.view(torch.float16)
+                dense_out = torch.empty((M, N), dtype=torch.float16, device=dev)
+                calls = {"spmm": lambda: sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, split_k),
+                         "cublas_dense": lambda: torch.matmul(Ad, Bh, out=dense_out)}
                 times = {}
-                for label, fn in (("spmm", lambda: sp.SpMM_SplitK_API(None, None, wd, None, None, od, Bd, Cd, M, N, K, ws, 2)),
-                                  ("cublas_dense", lambda: torch.matmul(Ad, Bd.view(torch.float16)))):
-                    for _ in range(3):
-                        fn()
-                    torch.cuda.synchronize()
-                    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-                    reps = 5
-                    e0.record()
-                    for _ in range(reps):
-                        fn()
-                    e1.record()
-                    torch.cuda.synchronize()
-                    times[label] = e0.elapsed_time(e1) * 1000.0 / reps
+                for label in ("spmm", "single_block", "cublas_dense"):
+                    fn = calls["spmm" if label == "single_block" else label]
+                    sp.set_pair_kernel(label != "single_block")
+                    times[label] = time_graph(torch, fn)
+                sp.set_pair_kernel(True)
                 flops = 2.0 * M * N * K
                 print(json.dumps({"M": M, "K": K, "N": N, "sparsity": p, "spmm_us": round(times["spmm"], 1),
+                                  "single_block_kernel_us": round(times["single_block"], 1),
                                   "cublas_dense_us": round(times["cublas_dense"], 1),
                                   "dense_equiv_tflops": round(flops / times["spmm"] / 1e6, 1),
                                   "frac_of_tensor_peak": round(flops / times["spmm"] / 1e6 / tensor_peak, 4),

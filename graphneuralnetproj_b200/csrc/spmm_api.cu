@@ -153,17 +153,12 @@ cudaError_t launch_decode(cudaStream_t stream, DeviceInfo& dev, int n_index, con
 // spmm_pair_kernel.cuh); spmm_b200_set_pair_kernel(0) keeps them on the single-block kernel.
 std::atomic<int> g_pair_kernel{1};
 
-#ifndef PAIR_SA2
-#define PAIR_SA2 8
-#define PAIR_SB2 3
-#define PAIR_SA1 8
-#define PAIR_SB1 5
-#endif
+// Eight decoder warps with an A buffer each, as at decode sizes (fewer decoders, or teams of two warps, were
+// measured slower); what is left of shared memory holds B buffers (of NM * 16 KB).
 template<int NM>
 struct PairConfig {
-    static constexpr int SA = NM == 2 ? PAIR_SA2 : PAIR_SA1;
-    static constexpr int SB = NM == 2 ? PAIR_SB2 : PAIR_SB1;
-    static constexpr int D = SA, VPL = 14;
+    static constexpr int SA = 8, D = 8, VPL = 14;
+    static constexpr int SB = NM == 2 ? 3 : 5;
 };
 
 // How many clusters of two blocks of the pair kernel the device holds at once (0: cannot run it).
@@ -922,17 +917,6 @@ int spmm_b200_spmm_splitk_token_major(void*       stream,
                                             static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global,
                                             K_Global, static_cast<half*>(Reduction_Workspace), Split_K));
 }
-
-#ifdef SPMM_PAIR_TIMING
-extern "C" int spmm_b200_pair_timing(unsigned long long* out)
-{
-    return static_cast<int>(cudaMemcpyFromSymbol(out, spmm_b200::g_pair_timing, sizeof(unsigned long long) * 512 * 24));
-}
-extern "C" int spmm_b200_pair_events(unsigned long long* out)
-{
-    return static_cast<int>(cudaMemcpyFromSymbol(out, spmm_b200::g_pair_events, sizeof(unsigned long long) * 2 * 160 * 8));
-}
-#endif
 
 int spmm_b200_set_pair_kernel(int enabled)
 {

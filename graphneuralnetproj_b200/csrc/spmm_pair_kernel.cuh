@@ -14,7 +14,9 @@
 //     decoded once per 512 columns instead of once per 256.  The accumulators then fill the 512 TMEM
 //     columns and the epilogue of a row no longer overlaps the next row (about 2 % at K = 12288).
 // Per block and restored tile at NM = 2: 450 (decode) + 2 * (128 + 128) (operands) = 962 wavefronts for
-// 1024 cycles of MMA, against 450 + 384 = 834 for 512 cycles in the single-block kernel.
+// 1024 cycles of MMA, against 450 + 384 = 834 for 512 cycles in the single-block kernel.  Measured on
+// 12288 x 12288 at 80 % sparsity (workspace for Split_K = 8): 71 / 129 / 217 / 403 us at N = 256 / 512 /
+// 1024 / 2048 against 87 / 147 / 290 / 543 us for the single-block kernel.
 //
 // Roles per block: warps 0..3 epilogue; warp 4 allocates TMEM and, in the even block (the leader),
 // issues the pair MMAs; warp 5 issues the tiled TMA loads of the block's half of the B slices, buffer
@@ -32,21 +34,6 @@
 
 namespace spmm_b200 {
 
-#ifdef SPMM_PAIR_TIMING
-__device__ unsigned long long g_pair_timing[512][24];
-__device__ unsigned long long g_pair_events[2][160][8];
-#define PAIR_EV(l, e) do { if (blockIdx.x < 2 && blockIdx.y == 0 && (l) < 160) g_pair_events[blockIdx.x][l][e] = ptx::global_timer_ns(); } while (0)
-#define PAIR_ACC(i, expr) do { const unsigned long long t_ = ptx::global_timer_ns(); expr; acc_[i] += ptx::global_timer_ns() - t_; } while (0)
-#define PAIR_ACC_DECL unsigned long long acc_[6] = {0, 0, 0, 0, 0, 0}
-#define PAIR_ACC_STORE(base, n, cond) do { if (cond) for (int i_ = 0; i_ < n; i_++) g_pair_timing[blockIdx.x + gridDim.x * blockIdx.y][base + i_] = acc_[i_]; } while (0)
-#define PAIR_T(i) do { if (warp == 0 && lane == 0) g_pair_timing[blockIdx.x + gridDim.x * blockIdx.y][i] = ptx::global_timer_ns(); } while (0)
-#else
-#define PAIR_T(i) do { } while (0)
-#define PAIR_EV(l, e) do { } while (0)
-#define PAIR_ACC(i, expr) do { expr; } while (0)
-#define PAIR_ACC_DECL
-#define PAIR_ACC_STORE(base, n, cond)
-#endif
 constexpr int kPairColsPerMma = 256;  // columns of one pair MMA; each block stages half of them
 
 // SA buffers for restored tiles of A, SB buffers for this block's half of a B slice (NM * 16 KB each)
@@ -149,9 +136,9 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
         // ------------------------------------------------------------ decoder warp (see spmm_decode_kernel)
         const int      s_own         = warp - kFirstDecodeWarp;  // this warp's first tile and first A buffer
         const uint32_t leader_ready0 = ptx::map_to_cta(ready(0), 0);
-        uint32_t  slot  = s_own;
-        uint4     r[VPL];
-        int       nvec = 0, next0 = 0, next1 = 0;
+        uint32_t       slot          = s_own;
+        uint4          r[VPL];
+        int            nvec = 0, next0 = 0, next1 = 0;
         auto load_words = [&](const uint4* from, int count) {
             if (count <= 0)
                 return;
@@ -190,7 +177,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             request_words(s_own + 2 * D);
         }
         ptx::grid_dependency_wait();
-        PAIR_ACC_DECL;
 #pragma unroll 1
         for (int l = s_own; l < num_tiles; l += D) {
             const bool     has_next = l + D < num_tiles;
@@ -198,22 +184,18 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             uint8_t* const a_tile   = smem_generic + slot * kATileBytes;
             request_words(l + 3 * D);
             if (before >= 0) {
-                bool ok_;
-                PAIR_ACC(0, ok_ = ptx::mbar_wait_bounded_cluster(done(before % R), (before / R) & 1, abort_word));
-                if (!ok_)
+                if (!ptx::mbar_wait_bounded_cluster(done(before % R), (before / R) & 1, abort_word))
                     break;
-                PAIR_ACC(1, {
 #pragma unroll
                 for (int i = 0; i < kATileBytes / (32 * 16); i++)
                     ptx::st_shared_zero_128(a_base + slot * kATileBytes + lane * 16u + i * 512u);
-                __syncwarp(); });
+                __syncwarp();  // the whole buffer is clear before any lane scatters into it
             }
-            if (lane == 0) PAIR_EV(l, 0);
-            PAIR_ACC(2, scatter_batch(a_tile, nvec); __syncwarp());
+            scatter_batch(a_tile, nvec);
 #pragma unroll 1
-            for (int done = VPL * 32; done < nvec; done += VPL * 32) {
-                load_words(src + done, nvec - done);
-                scatter_batch(a_tile, nvec - done);
+            for (int held = VPL * 32; held < nvec; held += VPL * 32) {  // tiles denser than the register budget
+                load_words(src + held, nvec - held);
+                scatter_batch(a_tile, nvec - held);
             }
             if (has_next) {
                 nvec = next1 - next0;
@@ -228,7 +210,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             ptx::fence_proxy_async_smem();
             __syncwarp();
             if (lane == 0) {
-                PAIR_EV(l, 1);
                 if (rank == 0)
                     ptx::mbar_arrive(ready(l % R));
                 else
@@ -238,7 +219,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             if (slot >= SA)
                 slot -= SA;
         }
-        PAIR_ACC_STORE(8, 3, s_own == 0 && lane == 0);
     }
     else if (warp == kLoaderWarp) {
         // ------------------------------------------------------------ B loader: this block's half of every slice
@@ -248,17 +228,12 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
         if (lane == 0) {
             const uint32_t leader_ready0 = ptx::map_to_cta(ready(0), 0);
             int j = tile_begin % tiles_k;
-            PAIR_ACC_DECL;
 #pragma unroll 1
             for (int l = 0; l < num_tiles; l++) {
                 // B buffer l % SB was last read by tile l - SB: wait for that tile's MMAs
                 const int s = l % SB;
-                bool ok_ = true;
-                if (l >= SB)
-                    PAIR_ACC(0, ok_ = ptx::mbar_wait_bounded_cluster(done((l - SB) % R), ((l - SB) / R) & 1, abort_word));
-                if (!ok_)
+                if (l >= SB && !ptx::mbar_wait_bounded_cluster(done((l - SB) % R), ((l - SB) / R) & 1, abort_word))
                     break;
-                PAIR_EV(l, 2);
                 // the bytes of both halves are counted on the leader's barrier, announced by the leader's loader
                 const uint32_t bar = leader_ready0 + 8u * (l % R);
                 if (rank == 0)
@@ -274,7 +249,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 if (++j == tiles_k)
                     j = 0;
             }
-            PAIR_ACC_STORE(16, 1, true);
         }
     }
     else if (warp == kFirstMmaWarp) {
@@ -284,11 +258,10 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(2 * kTileRows, kPairColsPerMma, false, true);
             const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
             const uint64_t     b_desc0 = ptx::make_smem_desc(b_base, BT::kLeadingBytes, BT::kGroupBytes, BT::kSwizzleMode);
-            const uint32_t     partner_done0      = ptx::map_to_cta(done(0), 1);
-            const uint32_t     partner_acc_full0  = ptx::map_to_cta(acc_full(0), 1);
+            const uint32_t     partner_done0     = ptx::map_to_cta(done(0), 1);
+            const uint32_t     partner_acc_full0 = ptx::map_to_cta(acc_full(0), 1);
             bool ok  = true;
             int  seg = 0;
-            PAIR_ACC_DECL;
 #pragma unroll 1
             for (int l0 = 0; l0 < num_tiles && ok; ++seg) {
                 const int j0  = (tile_begin + l0) % tiles_k;
@@ -296,15 +269,13 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 const int set = seg % ACC, use = seg / ACC;
                 const uint32_t d_tmem = tmem_base + set * NBLK;
                 if (use >= 1)
-                    PAIR_ACC(3, ok = ptx::mbar_wait_bounded_cluster(acc_free(set), (use - 1) & 1, abort_word));
+                    ok = ptx::mbar_wait_bounded_cluster(acc_free(set), (use - 1) & 1, abort_word);
                 uint32_t accumulate = 0;
 #pragma unroll 1
                 for (int l = l0; l < l0 + len && ok; l++) {
                     const int      sa = l % SA, sb = l % SB, e = l % R;
                     const uint32_t parity = (l / R) & 1;
-                    PAIR_EV(l, 4);
-                    PAIR_ACC(0, ok = ptx::mbar_wait_bounded_cluster(ready(e), parity, abort_word));
-                    PAIR_EV(l, 5);
+                    ok = ptx::mbar_wait_bounded_cluster(ready(e), parity, abort_word);
                     if (!ok)
                         break;
                     ptx::tc_fence_after_sync();
@@ -323,7 +294,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                     }
                     ptx::umma_commit_pair(done(e));
                     ptx::umma_commit_pair(partner_done0 + 8u * e);
-                    PAIR_EV(l, 6);
                     accumulate = 1;
                 }
                 if (ok) {
@@ -332,7 +302,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 }
                 l0 += len;
             }
-            PAIR_ACC_STORE(12, 4, true);
         }
     }
     else {
@@ -341,7 +310,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
         const uint32_t leader_acc_free0 = ptx::map_to_cta(acc_free(0), 0);
         int            seg              = 0;
         ptx::grid_dependency_wait();
-        PAIR_T(0);
         constexpr int CH = 16;
 #pragma unroll 1
         for (int l = 0; l < num_tiles; ++seg) {
@@ -355,7 +323,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             if (!warp_wait(acc_full(set), use & 1, abort_word, lane))
                 break;
             ptx::tc_fence_after_sync();
-            PAIR_T(1);
             auto load_chunk = [&](int c, float* out) {
                 ptx::tmem_ld_x16(tmem_base + set * NBLK + c * CH + (static_cast<uint32_t>(warp * 32) << 16),
                                  reinterpret_cast<uint32_t*>(out));
@@ -415,7 +382,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                     for (int i = 0; i < CH / 4; i++)
                         __stcg(mine + (c * (CH / 4) + i) * kTileRows, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
                 }
-                PAIR_T(2);
                 __threadfence();
                 __syncwarp();
                 unsigned int  arrived = 0;
@@ -424,7 +390,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 if (lane == 0)
                     arrived = atomicAdd(counter, 1u);
                 arrived = __shfl_sync(0xffffffffu, arrived, 0);
-                PAIR_T(3);
                 if (arrived == static_cast<unsigned int>(g_last - g_first)) {
                     if (lane == 0)
                         *counter = 0;
@@ -476,7 +441,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                     }
                 }
             }
-            PAIR_T(4);
             // only now may the leader overwrite this accumulator set (in both blocks)
             ptx::tmem_ld_wait();
             ptx::tc_fence_before_sync();
@@ -490,7 +454,6 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
     // ---------------------------------------------------------------- exit
     ptx::tc_fence_before_sync();
     __syncthreads();
-    PAIR_T(5);
     if (threadIdx.x == 0 && *abort_word != 0)
         atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
     // Neither block leaves while its partner may still arrive on its barriers or the leader's MMAs may

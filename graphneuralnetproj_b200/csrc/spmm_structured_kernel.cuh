@@ -328,15 +328,18 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
                     g_first--;
                 while (p.sched.chunk_begin[g_last + 1] < (row_tile + 1) * tiles_k)
                     g_last++;
-                float* mine = p.slots + (static_cast<size_t>(cta + above) * kTileRows + row_in_tile) * N;
+                // slots as [N / 4 groups of four columns][128 rows] float4: a warp's 32 rows are contiguous (see spmm_decode_kernel)
+                auto slot_of = [&](int g) {
+                    return reinterpret_cast<float4*>(p.slots) + static_cast<size_t>(g + above) * (kTileRows * N / 4) + row_in_tile;
+                };
+                float4* const mine = slot_of(cta);
 #pragma unroll 1
                 for (int c = 0; c < N / CH; c++) {
                     float v[CH];
                     load_chunk(c, v);
 #pragma unroll
                     for (int i = 0; i < CH / 4; i++)
-                        __stcg(reinterpret_cast<float4*>(mine + c * CH) + i,
-                               make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                        __stcg(mine + (c * (CH / 4) + i) * kTileRows, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
                 }
                 __threadfence();
                 __syncwarp();
@@ -364,11 +367,10 @@ __global__ void __launch_bounds__(kStructuredThreads, 1) spmm_structured_kernel(
                                     sum[n] += own[n];
                             }
                             else {
-                                const float4* theirs = reinterpret_cast<const float4*>(
-                                    p.slots + (static_cast<size_t>(g + above) * kTileRows + row_in_tile) * N + c * CH);
+                                const float4* theirs = slot_of(g) + c * (CH / 4) * kTileRows;
 #pragma unroll
                                 for (int i = 0; i < CH / 4; i++) {
-                                    const float4 x = __ldcg(theirs + i);
+                                    const float4 x = __ldcg(theirs + i * kTileRows);
                                     sum[4 * i] += x.x;
                                     sum[4 * i + 1] += x.y;
                                     sum[4 * i + 2] += x.z;

@@ -245,6 +245,9 @@ int spmm_b200_set_weights_constant(int constant);
  * slice; with N a multiple of 512 a restored tile serves 512 columns).  0 keeps such calls on the
  * single-block kernel that serves every other width (for comparison; the results of the two agree
  * within rounding, not bit for bit, because rows are split between blocks at different k).
+ * At these widths a partial tile is 128 x 256 or 128 x 512 floats, so the workspace decides how many
+ * rows can be split between SMs: size it with the Split_K that spmm_b200_suggest_split_k returns
+ * (with less the call still succeeds, on fewer SMs).
  * Process-wide; returns the previous setting (default 1). */
 int spmm_b200_set_pair_kernel(int enabled);
 
