@@ -182,7 +182,7 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tenso
 // The same load issued by either block of a pair (a cluster of two): the box lands in the issuing block's
 // shared memory, the bytes are counted on an mbarrier of either block (`bar_cluster`: address in the
 // cluster's shared window, see map_to_cta), which is how the partner's half of an operand is reported to
-// the block that issues the pair's MMAs.  No multicast: every block fetches what it stages itself.
+// the block that issues the pair's MMAs.  Every block fetches what it stages itself; nothing is broadcast.
 __device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tensor_map, int x, int y, uint32_t bar_cluster)
 {
     asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];" ::"r"(
