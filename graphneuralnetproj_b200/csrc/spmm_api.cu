@@ -766,9 +766,9 @@ namespace spmm_b200 {
 namespace {
 // Copy streams and events of spmm_b200_spmm_splitk_host_io_batch, created on first use, one set per device.
 struct HostIoLanes {
-    bool         ready = false;
+    bool         ready = false, have_previous = false;
     cudaStream_t in = nullptr, out = nullptr;
-    cudaEvent_t  fork = nullptr, joined = nullptr;
+    cudaEvent_t  fork = nullptr, joined = nullptr, products = nullptr;
     cudaEvent_t  landed[SPMM_B200_HOST_IO_MAX_ITEMS] = {};
     cudaEvent_t  multiplied[SPMM_B200_HOST_IO_MAX_ITEMS] = {};
 };
@@ -786,6 +786,8 @@ cudaError_t host_io_lanes(int device, HostIoLanes** out)
             e = cudaEventCreateWithFlags(&lanes.fork, cudaEventDisableTiming);
         if (e == cudaSuccess)
             e = cudaEventCreateWithFlags(&lanes.joined, cudaEventDisableTiming);
+        if (e == cudaSuccess)
+            e = cudaEventCreateWithFlags(&lanes.products, cudaEventDisableTiming);
         for (int i = 0; i < SPMM_B200_HOST_IO_MAX_ITEMS && e == cudaSuccess; i++) {
             e = cudaEventCreateWithFlags(&lanes.landed[i], cudaEventDisableTiming);
             if (e == cudaSuccess)
@@ -826,10 +828,16 @@ int spmm_b200_spmm_splitk_host_io_batch(void* stream, int count, const spmm_b200
         if (e != cudaSuccess)              \
             return static_cast<int>(e);    \
     } while (0)
-    // the copies start once everything queued on `stream` so far has finished with the buffers
-    SPMM_B200_TRY(cudaEventRecord(lanes->fork, st));
-    SPMM_B200_TRY(cudaStreamWaitEvent(lanes->in, lanes->fork, 0));
-    SPMM_B200_TRY(cudaStreamWaitEvent(lanes->out, lanes->fork, 0));
+    // The copies in start once the staging buffers are free: after everything queued on `stream` so far (first call),
+    // or after the products of the previous call (later calls: its copies out may still be under way, so the
+    // activations of this call travel while the last results of the previous one do).  The copies out follow their
+    // products, which follow `stream`.
+    if (!lanes->have_previous) {
+        SPMM_B200_TRY(cudaEventRecord(lanes->fork, st));
+        SPMM_B200_TRY(cudaStreamWaitEvent(lanes->in, lanes->fork, 0));
+    }
+    else
+        SPMM_B200_TRY(cudaStreamWaitEvent(lanes->in, lanes->products, 0));
     for (int i = 0; i < count; i++) {
         const spmm_b200_host_io_item& it = items[i];
         SPMM_B200_TRY(cudaMemcpyAsync(it.B_dev, it.B_host, static_cast<size_t>(it.K) * it.N * sizeof(half),
@@ -847,6 +855,8 @@ int spmm_b200_spmm_splitk_host_io_batch(void* stream, int count, const spmm_b200
         SPMM_B200_TRY(cudaMemcpyAsync(it.C_host, it.C_dev, static_cast<size_t>(it.M) * it.N * sizeof(half),
                                       cudaMemcpyDeviceToHost, lanes->out));
     }
+    SPMM_B200_TRY(cudaEventRecord(lanes->products, st));
+    lanes->have_previous = true;
     SPMM_B200_TRY(cudaEventRecord(lanes->joined, lanes->out));
     SPMM_B200_TRY(cudaStreamWaitEvent(st, lanes->joined, 0));
 #undef SPMM_B200_TRY

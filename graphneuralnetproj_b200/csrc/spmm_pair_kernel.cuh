@@ -26,8 +26,9 @@
 // lane waits once per tile (a lane in the partner that forwarded its block's readiness was measured to
 // take 0.6 us per tile, more than the MMAs of a tile); the leader's tcgen05.commit arrives on the
 // "done" / acc_full barriers of both blocks (one commit per block, the second through the cluster-window
-// address of the partner's barrier); the partner's epilogue warps arrive on the leader's acc_free barrier.  Every wait is bounded; a block that gives up still
-// reaches the cluster barrier at the end, so its partner never waits for it without limit.
+// address of the partner's barrier); the partner's epilogue warps arrive on the leader's acc_free
+// barrier.  Every wait is bounded; a block that gives up still reaches the cluster barrier at the end,
+// so its partner never waits for it without limit.
 #pragma once
 
 #include "spmm_decode_kernel.cuh"

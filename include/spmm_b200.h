@@ -75,7 +75,10 @@ int spmm_b200_spmm_splitk_host_io(void*       stream,
  * synchronising `stream` (or queueing more work on it) is enough to read C_host.  The library keeps
  * two streams and a few events per device for this (created by the first call on the device, which
  * should not fall inside a stream capture).  count: 1 .. SPMM_B200_HOST_IO_MAX_ITEMS.  Calls are
- * serialised by a lock.  Returns the first cudaError_t met, as an int.  The reference's harness
+ * serialised by a lock.  The staging buffers B_dev and C_dev belong to these calls: the copies in of a
+ * call are ordered after the products of the previous call on the device (so they travel while that
+ * call's last results still go out), not after other work the caller queued on `stream` in between;
+ * a caller that touches B_dev or C_dev itself synchronises first.  Returns the first cudaError_t met, as an int.  The reference's harness
  * does the same copies with blocking cudaMemcpy calls (kernel_benchmark/spmm_test.cu:118-137,
  * 565-567). */
 #define SPMM_B200_HOST_IO_MAX_ITEMS 16

@@ -33,7 +33,13 @@ def build():
     directory named `reference` beside this repository), the reference libraries."""
     beside = os.path.join(os.path.dirname(os.path.dirname(_HERE)), "reference")
     root = os.environ.get("REFERENCE_ROOT") or (beside if os.path.isfile(os.path.join(beside, "csrc", "SpMM_API.cu")) else "")
-    subprocess.check_call(["make", "-s", "-C", _HERE] + (["REFERENCE_ROOT=" + root] if root else []))
+    import fcntl
+    with open(os.path.join(_HERE, ".build.lock"), "w") as lock:  # several ranks of one job may get here at once
+        fcntl.flock(lock, fcntl.LOCK_EX)
+        try:
+            subprocess.check_call(["make", "-s", "-C", _HERE] + (["REFERENCE_ROOT=" + root] if root else []))
+        finally:
+            fcntl.flock(lock, fcntl.LOCK_UN)
 
 
 _lib = None

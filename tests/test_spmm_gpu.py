@@ -271,6 +271,44 @@ def test_host_buffer_entry_point(sp, oracle, torch_cuda):
     assert np.array_equal(C_host.numpy().view(np.uint16), want)
 
 
+def test_host_buffer_batches_back_to_back_share_staging_buffers(sp, oracle, torch_cuda):
+    """Batches of two products queued one after the other without a synchronisation in between, each with its
+    own activations and results in page-locked host memory but all through the same device staging buffers: the
+    copies in of a batch must wait for the products of the batch before it, its products for that batch's copies
+    out.  Every batch must give the result of the device-pointer call on its own activations."""
+    torch = torch_cuda
+    dev = torch.device("cuda:0")
+    shapes = [(1152, 2304), (2304, 1152)]
+    N, sk, batches = 16, 8, 4
+    layers = []
+    for li, (M, K) in enumerate(shapes):
+        A = sp.synth_fp16((M, K), 910 + li, 0.02, 0.8)
+        words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+        layers.append(dict(M=M, K=K, words=words, offsets=offsets,
+                           wd=torch.from_numpy(words.view(np.int32)).to(dev), od=torch.from_numpy(offsets).to(dev),
+                           B_dev=torch.zeros((K, N), dtype=torch.int16, device=dev),
+                           C_dev=torch.zeros((M, N), dtype=torch.int16, device=dev),
+                           ws=torch.zeros(sp.workspace_bytes(M, N, sk) // 2, dtype=torch.int16, device=dev)))
+    B = [[sp.synth_fp16((L["K"], N), 920 + 10 * b + li, 1.0, 0.0) for li, L in enumerate(layers)] for b in range(batches)]
+    want = [[run_spmm(sp, torch, L["words"], L["offsets"], B[b][li], L["M"], N, L["K"], sk) for li, L in enumerate(layers)]
+            for b in range(batches)]
+    B_host = [[torch.from_numpy(B[b][li].view(np.int16)).pin_memory() for li in range(len(layers))] for b in range(batches)]
+    C_host = [[torch.zeros((L["M"], N), dtype=torch.int16).pin_memory() for L in layers] for b in range(batches)]
+    items = [sp.host_io_items([dict(Compressed_A=L["wd"], TileOffsets=L["od"], B_host=B_host[b][li], C_host=C_host[b][li],
+                                    B_dev=L["B_dev"], C_dev=L["C_dev"], M=L["M"], N=N, K=L["K"],
+                                    Reduction_Workspace=L["ws"], Split_K=sk) for li, L in enumerate(layers)])
+             for b in range(batches)]
+    stream = torch.cuda.Stream()
+    for _ in range(2):  # the second round starts with results of the first still on their way out
+        for b in range(batches):
+            assert sp.SpMM_SplitK_API_host_io_batch(stream, items[b]) == 0
+    stream.synchronize()
+    assert sp.device_status() == 0
+    for b in range(batches):
+        for li in range(len(layers)):
+            assert np.array_equal(C_host[b][li].numpy().view(np.uint16), want[b][li]), (b, li)
+
+
 def test_a_wait_that_runs_out_is_reported_not_hung(sp, oracle, torch_cuda):
     """Failure detection without a fault: a kernel waits on a barrier nothing arrives on; the bounded
     wait gives up after 50 ms, the kernel returns, the status word says so, and the device keeps working."""
