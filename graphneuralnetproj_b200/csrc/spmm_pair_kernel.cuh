@@ -50,6 +50,69 @@ constexpr int pair_threads()
     return (kFirstMmaWarp + 2 + D) * 32;
 }
 
+// Adds the parked partial rows of one output row -- `owners` slots, 2 * slot4 float4 apart, in owner order -- and
+// writes the fp16 result: the chunks first, first + step, ... of 16 columns.  `parked` points at the row's float4 in
+// the first owner's slot (slots are [NBLK / 4][128 rows] float4); four owners' loads are in flight together.
+template<int NBLK>
+__device__ __forceinline__ void sum_parked_row(const float4* parked, size_t slot4, int owners, half* c_row, int first, int step)
+{
+    constexpr int CH = 16;
+#pragma unroll 1
+    for (int c = first; c < NBLK / CH; c += step) {
+        float sum[CH];
+#pragma unroll
+        for (int n = 0; n < CH; n++)
+            sum[n] = 0.0f;
+#pragma unroll 1
+        for (int k0 = 0; k0 < owners; k0 += 4) {
+            float4 part[4][CH / 4];
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (k0 + u < owners) {
+                    const float4* src = parked + static_cast<size_t>(k0 + u) * 2 * slot4 + c * (CH / 4) * kTileRows;
+#pragma unroll
+                    for (int i = 0; i < CH / 4; i++)
+                        part[u][i] = __ldcg(src + i * kTileRows);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                if (k0 + u >= owners)
+                    break;
+#pragma unroll
+                for (int i = 0; i < CH / 4; i++) {
+                    sum[4 * i] += part[u][i].x;
+                    sum[4 * i + 1] += part[u][i].y;
+                    sum[4 * i + 2] += part[u][i].z;
+                    sum[4 * i + 3] += part[u][i].w;
+                }
+            }
+        }
+        uint4* dst = reinterpret_cast<uint4*>(c_row + c * CH);
+#pragma unroll
+        for (int i = 0; i < CH / 8; i++) {
+            __half2 h0 = __floats2half2_rn(sum[8 * i], sum[8 * i + 1]);
+            __half2 h1 = __floats2half2_rn(sum[8 * i + 2], sum[8 * i + 3]);
+            __half2 h2 = __floats2half2_rn(sum[8 * i + 4], sum[8 * i + 5]);
+            __half2 h3 = __floats2half2_rn(sum[8 * i + 6], sum[8 * i + 7]);
+            uint4   o;
+            o.x    = *reinterpret_cast<uint32_t*>(&h0);
+            o.y    = *reinterpret_cast<uint32_t*>(&h1);
+            o.z    = *reinterpret_cast<uint32_t*>(&h2);
+            o.w    = *reinterpret_cast<uint32_t*>(&h3);
+            dst[i] = o;
+        }
+    }
+}
+
+// What the last arriver of the chunk's final row leaves for the whole block to sum on the way out.
+struct PendingSum {
+    int mask;        // quarters (epilogue warps) of the row of tiles whose sum is pending
+    int row_tile;    // the row of tiles
+    int first_slot;  // this block's slot of the first owner
+    int owners;
+};
+
 // NM  : pair MMAs per k step = 256-column blocks served by one restored tile (1 or 2); the cluster
 //       handles NM * 256 columns (blockIdx.y selects which)
 // D   : decoder warps (tile l of the chunk is restored by warp l % D into A buffer l % SA), each holding
@@ -86,7 +149,8 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
     uint8_t*       smem_generic   = smem_raw + (smem_base - ptx::smem_addr(smem_raw));
     volatile uint32_t* tmem_slot  = reinterpret_cast<volatile uint32_t*>(smem_generic + (tmem_slot_addr - smem_base));
     volatile int*      abort_word = reinterpret_cast<volatile int*>(smem_generic + (tmem_slot_addr + 4 - smem_base));
-    static_assert(8 * (2 * R + 4) + 8 <= 512, "barrier block");
+    PendingSum* const  pending    = reinterpret_cast<PendingSum*>(smem_generic + (bar_base + 384 - smem_base));
+    static_assert(8 * (2 * R + 4) + 8 <= 384, "barrier block");
     static_assert(SA >= D, "every decoder warp needs a buffer of its own to start with");
     static_assert(NM == 1 || NM == 2, "one or two 256-column MMAs per k step");
 
@@ -117,7 +181,8 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
             ptx::mbar_init(acc_full(b), 1);
             ptx::mbar_init(acc_free(b), 2 * kEpilogueWarps);
         }
-        *abort_word = 0;
+        *abort_word   = 0;
+        pending->mask = 0;
         ptx::mbar_init_fence();
     }
     for (uint32_t off = threadIdx.x * 16u; off < static_cast<uint32_t>(SA * kATileBytes + SB * NM * BT::kBytes); off += blockDim.x * 16u)
@@ -391,56 +456,38 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 if (lane == 0)
                     arrived = atomicAdd(counter, 1u);
                 arrived = __shfl_sync(0xffffffffu, arrived, 0);
+                // The partial rows are parked, so the accumulators are free: the leader may start the next row of
+                // tiles while the last arriver adds the owners' slots -- its own included -- out of memory.
+                ptx::tmem_ld_wait();
+                ptx::tc_fence_before_sync();
+                __syncwarp();
+                if (lane == 0)
+                    ptx::mbar_arrive_cluster(leader_acc_free0 + 8u * set);
                 if (arrived == static_cast<unsigned int>(g_last - g_first)) {
                     if (lane == 0)
                         *counter = 0;
                     __threadfence();
-#pragma unroll 1
-                    for (int c = 0; c < NBLK / CH; c++) {
-                        float own[CH], sum[CH];
-                        load_chunk(c, own);
-#pragma unroll
-                        for (int n = 0; n < CH; n++)
-                            sum[n] = 0.0f;
-                        // the other owners' slots, four owners at a time: their loads are issued together, the
-                        // sums follow in owner order
-#pragma unroll 1
-                        for (int g0 = g_first; g0 <= g_last; g0 += 4) {
-                            float4 theirs[4][CH / 4];
-#pragma unroll
-                            for (int u = 0; u < 4; u++) {
-                                const int g = g0 + u;
-                                if (g <= g_last && g != cluster) {
-                                    const float4* src = slot_of(g) + c * (CH / 4) * kTileRows;
-#pragma unroll
-                                    for (int i = 0; i < CH / 4; i++)
-                                        theirs[u][i] = __ldcg(src + i * kTileRows);
-                                }
-                            }
-#pragma unroll
-                            for (int u = 0; u < 4; u++) {
-                                const int g = g0 + u;
-                                if (g > g_last)
-                                    break;
-                                if (g == cluster) {
-#pragma unroll
-                                    for (int n = 0; n < CH; n++)
-                                        sum[n] += own[n];
-                                }
-                                else {
-#pragma unroll
-                                    for (int i = 0; i < CH / 4; i++) {
-                                        sum[4 * i] += theirs[u][i].x;
-                                        sum[4 * i + 1] += theirs[u][i].y;
-                                        sum[4 * i + 2] += theirs[u][i].z;
-                                        sum[4 * i + 3] += theirs[u][i].w;
-                                    }
-                                }
-                            }
+                    const int first_slot = (g_first + above) * 2 + static_cast<int>(rank);
+                    if (l + len == num_tiles) {
+                        // the chunk's final row: nothing is left to overlap with, so all warps of the block share the
+                        // sum on the way out (one warp per quarter would make 32 L2 round trips in a row)
+                        if (lane == 0) {
+                            pending->row_tile   = row_tile;
+                            pending->first_slot = first_slot;
+                            pending->owners     = g_last - g_first + 1;
+                            atomicOr(&pending->mask, 1 << warp);
                         }
-                        store_c_chunk(c, sum);
                     }
+                    else
+                        sum_parked_row<NBLK>(reinterpret_cast<const float4*>(slots) + static_cast<size_t>(first_slot) * (kTileRows * NBLK / 4)
+                                                 + row_in_tile,
+                                             kTileRows * NBLK / 4, g_last - g_first + 1,
+                                             p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
+                                                 + static_cast<size_t>(blockIdx.y) * NBLK,
+                                             0, 1);
                 }
+                l += len;
+                continue;
             }
             // only now may the leader overwrite this accumulator set (in both blocks)
             ptx::tmem_ld_wait();
@@ -457,6 +504,19 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
     __syncthreads();
     if (threadIdx.x == 0 && *abort_word != 0)
         atomicExch(&g_device_status, static_cast<int>(kStatusWaitTimeout));
+    if (const int mask = *reinterpret_cast<volatile int*>(&pending->mask)) {
+        const float4* slots4 = reinterpret_cast<const float4*>(p.slots)
+                               + static_cast<size_t>(blockIdx.y) * p.slots_per_block_column * (kTileRows * NBLK / 4);
+        for (int quarter = 0; quarter < kEpilogueWarps; quarter++)
+            if ((mask >> quarter) & 1) {
+                const int row = quarter * 32 + lane;
+                sum_parked_row<NBLK>(slots4 + static_cast<size_t>(pending->first_slot) * (kTileRows * NBLK / 4) + row,
+                                     kTileRows * NBLK / 4, pending->owners,
+                                     p.C + (static_cast<size_t>(pending->row_tile) * kTileRows + row) * p.ld
+                                         + static_cast<size_t>(blockIdx.y) * NBLK,
+                                     warp, static_cast<int>(blockDim.x) / 32);
+            }
+    }
     // Neither block leaves while its partner may still arrive on its barriers or the leader's MMAs may
     // still read its shared memory (a block that gave up gets here too).
     ptx::cluster_sync_all();
