@@ -39,8 +39,8 @@ struct DecodeConfig {
 
 struct DeviceInfo {
     int  sm_count = 0;
-    bool attrs_set[16] = {};  // cudaFuncSetAttribute done, per kernel instantiation
-    int  pair_clusters[2] = {};  // clusters of the pair kernel the device holds at once, per NM
+    bool attrs_set[20] = {};  // cudaFuncSetAttribute done, per kernel instantiation
+    int  pair_clusters[4] = {};  // clusters of the pair kernel the device holds at once, per layout and NM
 };
 
 std::mutex g_device_lock;  // guards DeviceInfo, the workspace -> counter set table and the caches below
@@ -162,13 +162,13 @@ struct PairConfig {
 };
 
 // How many clusters of two blocks of the pair kernel the device holds at once (0: cannot run it).
-template<int NM>
+template<int NM, int TM = 0>
 int pair_clusters(DeviceInfo& dev, int n_index)
 {
     using Cfg          = PairConfig<NM>;
     constexpr int smem = pair_smem_bytes<NM, Cfg::SA, Cfg::SB>();
     static_assert(smem <= 227 * 1024, "ring does not fit in shared memory");
-    auto kern = spmm_pair_kernel<NM, Cfg::D, Cfg::VPL, Cfg::SA, Cfg::SB>;
+    auto kern = spmm_pair_kernel<NM, Cfg::D, Cfg::VPL, Cfg::SA, Cfg::SB, TM>;
     std::lock_guard<std::mutex> guard(g_device_lock);
     if (!dev.attrs_set[n_index]) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem) != cudaSuccess) {
@@ -191,17 +191,17 @@ int pair_clusters(DeviceInfo& dev, int n_index)
             (void)cudaGetLastError();
             clusters = 0;
         }
-        dev.pair_clusters[NM - 1] = std::min(clusters, dev.sm_count / 2);
-        dev.attrs_set[n_index]    = true;
+        dev.pair_clusters[2 * TM + NM - 1] = std::min(clusters, dev.sm_count / 2);
+        dev.attrs_set[n_index]             = true;
     }
-    return dev.pair_clusters[NM - 1];
+    return dev.pair_clusters[2 * TM + NM - 1];
 }
 
-template<int NM>
+template<int NM, int TM = 0>
 cudaError_t launch_pair(cudaStream_t stream, const DecodeParams& params, int column_blocks)
 {
     using Cfg                 = PairConfig<NM>;
-    auto kern                 = spmm_pair_kernel<NM, Cfg::D, Cfg::VPL, Cfg::SA, Cfg::SB>;
+    auto kern                 = spmm_pair_kernel<NM, Cfg::D, Cfg::VPL, Cfg::SA, Cfg::SB, TM>;
     cudaLaunchConfig_t config = {};
     config.gridDim            = dim3(2 * params.sched.num_ctas, column_blocks);
     config.blockDim           = dim3(pair_threads<Cfg::D>());
@@ -286,6 +286,22 @@ cudaError_t describe_b(CUtensorMap& map, const half* B, int N_Global, int K_Glob
                 return cudaSuccess;
             }
     }
+    if (n_block < 0) {
+        // token-major B[N][K]: x = k, y = token; boxes of 64 k values x 128 tokens, rows of 128 bytes
+        const cuuint64_t dims[2]    = {static_cast<cuuint64_t>(K_Global), static_cast<cuuint64_t>(N_Global)};
+        const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K_Global) * sizeof(half)};
+        const cuuint32_t box[2]     = {static_cast<cuuint32_t>(kTileCols), static_cast<cuuint32_t>(kPairColsPerMma / 2)};
+        const cuuint32_t steps[2]   = {1, 1};
+        if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<half*>(B), dims, strides, box, steps,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE)
+            != CUDA_SUCCESS)
+            return cudaErrorInvalidValue;
+        std::lock_guard<std::mutex> guard(lock);
+        const int slot = used < kEntries ? used++ : (next++ % kEntries);
+        cache[slot]    = Entry{B, N_Global, K_Global, n_block, map};
+        return cudaSuccess;
+    }
     const int                box_cols = n_block < 16 ? 16 : (n_block > 64 ? 64 : n_block);
     const CUtensorMapSwizzle swizzle  = box_cols == 16   ? CU_TENSOR_MAP_SWIZZLE_32B
                                         : box_cols == 32 ? CU_TENSOR_MAP_SWIZZLE_64B
@@ -323,8 +339,8 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
                            const float* addend = nullptr, size_t workspace_skip_bytes = 0, const PeerSumParams* peer = nullptr)
 {
     // N: 8, 16, 32, 64 as in the reference (csrc/SpMM_API.cu:105-196); multiples of 64 beyond that are
-    // served by the same kernel, one 64-column block per blockIdx.y (row-major layout only).
-    const bool wide = N_Global > 64 && N_Global % 64 == 0 && N_Global <= 8192 && !token_major;
+    // served in column blocks (blockIdx.y) of 64 to 512 columns, in both layouts.
+    const bool wide = N_Global > 64 && N_Global % 64 == 0 && N_Global <= 8192;
     if (N_Global != 8 && N_Global != 16 && N_Global != 32 && N_Global != 64 && !wide) {
         printf("MM_Sparse_API Error: Unsupported N dimension %d!\n", N_Global);
         return cudaErrorUnknown;
@@ -346,14 +362,15 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
     if (wide && N_Global % 256 == 0 && M_Global % (2 * kTileRows) == 0 && addend == nullptr && peer == nullptr
         && g_pair_kernel.load(std::memory_order_relaxed) != 0) {
         pair_nm  = N_Global % 512 == 0 ? 2 : 1;
-        clusters = pair_nm == 2 ? pair_clusters<2>(dev, 15) : pair_clusters<1>(dev, 14);
+        clusters = token_major ? (pair_nm == 2 ? pair_clusters<2, 1>(dev, 17) : pair_clusters<1, 1>(dev, 16))
+                               : (pair_nm == 2 ? pair_clusters<2>(dev, 15) : pair_clusters<1>(dev, 14));
         if (clusters == 0)
             pair_nm = 0;
     }
     // the widest slice that divides N: the sparse tiles are decoded once per column block
     const int n_block       = !wide ? N_Global
                                     : (pair_nm ? pair_nm * kPairColsPerMma
-                                               : (N_Global % 256 == 0 ? 256 : (N_Global % 128 == 0 ? 128 : 64)));
+                                               : (token_major ? 64 : (N_Global % 256 == 0 ? 256 : (N_Global % 128 == 0 ? 128 : 64))));
     const int column_blocks = N_Global / n_block;
     if (static_cast<long>(M_Global / kTileRows) * column_blocks > kMaxRowTiles)
         return cudaErrorInvalidValue;
@@ -407,9 +424,11 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
         cached_schedule(PlanKey{tiles_m / 2, tiles_k, std::max(1, clusters / std::min(column_blocks, 4)), slots_granted / 2},
                         params.sched);
         params.slots_per_block_column = 2 * params.sched.slots_used;
-        e = describe_b(params.b_map, B, N_Global, K_Global, n_block);
+        e = describe_b(params.b_map, B, N_Global, K_Global, token_major ? -1 : n_block);
         if (e != cudaSuccess)
             return e;
+        if (token_major)
+            return pair_nm == 2 ? launch_pair<2, 1>(stream, params, column_blocks) : launch_pair<1, 1>(stream, params, column_blocks);
         return pair_nm == 2 ? launch_pair<2>(stream, params, column_blocks) : launch_pair<1>(stream, params, column_blocks);
     }
     // with several column blocks the blocks of one column share the SMs with the other columns
@@ -422,6 +441,8 @@ cudaError_t spmm_tiled_csl(cudaStream_t stream, const uint4* Compressed_A, const
         if (e != cudaSuccess)
             return e;
     }
+    if (wide && token_major)  // 64 tokens per column block
+        return launch_decode<64, 1>(stream, dev, 7, params, column_blocks);
     if (wide) {
         switch (n_block) {
             case 256:

@@ -314,7 +314,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             if (TM) {
                 // row n of the slice: 64 halves of token n starting at column 64 j (eight 16-byte chunks);
                 // chunk q of row n lands at n * 128 + ((q ^ (n % 8)) * 16)
-                const half* b_src = p.B + static_cast<size_t>(j) * kTileCols;
+                // (with several column blocks, blockIdx.y selects N tokens of B[n][K] and of C[n][M])
+                const half* b_src = p.B + static_cast<size_t>(blockIdx.y) * N * (static_cast<size_t>(tiles_k) * kTileCols)
+                                    + static_cast<size_t>(j) * kTileCols;
 #pragma unroll
                 for (int i = 0; i < (N * 8) / (WPT * 32); i++) {
                     const uint32_t c = first_chunk + i * WPT * 32;
@@ -605,7 +607,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             };
             auto store_c_chunk = [&](int c, const float* v) {
                 if (TM) {
-                    half* dst = p.C + static_cast<size_t>(row_tile) * kTileRows + row_in_tile;  // C[n][m]
+                    half* dst = p.C + static_cast<size_t>(blockIdx.y) * N * p.m + static_cast<size_t>(row_tile) * kTileRows
+                                + row_in_tile;  // C[n][m]
 #pragma unroll
                     for (int n = 0; n < CH; n++)
                         dst[static_cast<size_t>(c * CH + n) * p.m] = __float2half_rn(v[n]);

@@ -53,8 +53,11 @@ constexpr int pair_threads()
 // Adds the parked partial rows of one output row -- `owners` slots, 2 * slot4 float4 apart, in owner order -- and
 // writes the fp16 result: the chunks first, first + step, ... of 16 columns.  `parked` points at the row's float4 in
 // the first owner's slot (slots are [NBLK / 4][128 rows] float4); four owners' loads are in flight together.
-template<int NBLK>
-__device__ __forceinline__ void sum_parked_row(const float4* parked, size_t slot4, int owners, half* c_row, int first, int step)
+// TM: token-major results, C[n][m]: `c_row` then points at (row, first column of the block) and a column is
+// `m_stride` halves further.
+template<int NBLK, int TM>
+__device__ __forceinline__ void
+sum_parked_row(const float4* parked, size_t slot4, int owners, half* c_row, size_t m_stride, int first, int step)
 {
     constexpr int CH = 16;
 #pragma unroll 1
@@ -87,6 +90,12 @@ __device__ __forceinline__ void sum_parked_row(const float4* parked, size_t slot
                     sum[4 * i + 3] += part[u][i].w;
                 }
             }
+        }
+        if (TM) {
+#pragma unroll
+            for (int n = 0; n < CH; n++)
+                c_row[static_cast<size_t>(c * CH + n) * m_stride] = __float2half_rn(sum[n]);
+            continue;
         }
         uint4* dst = reinterpret_cast<uint4*>(c_row + c * CH);
 #pragma unroll
@@ -122,7 +131,10 @@ struct PendingSum {
 //       NM times larger than a restored tile, so fewer of them fit
 //       p.sched partitions (M / 256) rows of tile pairs x (K / 64) among the clusters;
 //       p.slots_per_block_column counts slots of 128 x (NM * 256) floats, two per schedule slot.
-template<int NM, int D, int VPL, int SA, int SB>
+// TM  : 1 = token-major activations and results, B[N][K] and C[N][M] (the FasterTransformer caller's layout,
+//       third_party/ft.patch:2822-2846): a block's half of a B slice is then 128 tokens x 64 k values, K-contiguous,
+//       one TMA box in the 128-byte-swizzle layout the restored A tiles have
+template<int NM, int D, int VPL, int SA, int SB, int TM>
 __global__ void __launch_bounds__(pair_threads<D>(), 1)
 spmm_pair_kernel(const __grid_constant__ DecodeParams p)
 {
@@ -168,6 +180,12 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
     auto tile_index = [&](int l) {
         const int t = tile_begin + l;
         return t + (t / tiles_k + static_cast<int>(rank)) * tiles_k;
+    };
+    // Where output row `row` of row of tiles `rt` starts in this cluster's columns: C[m][n] row-major, or C[n][m]
+    // (TM), where the next column is p.m halves further.
+    auto c_origin = [&](int rt, int row) {
+        const size_t m_index = static_cast<size_t>(rt) * kTileRows + row, n0 = static_cast<size_t>(blockIdx.y) * NBLK;
+        return TM ? p.C + n0 * p.m + m_index : p.C + m_index * p.ld + n0;
     };
     constexpr int kLoaderWarp      = kFirstMmaWarp + 1;
     constexpr int kFirstDecodeWarp = kFirstMmaWarp + 2;
@@ -305,13 +323,16 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 if (rank == 0)
                     ptx::mbar_arrive_expect_tx(ready(l % R), 2 * NM * BT::kBytes);
 #pragma unroll
-                for (int m = 0; m < NM; m++)
+                for (int m = 0; m < NM; m++) {
+                    const int col0 = static_cast<int>(blockIdx.y) * NBLK + m * kPairColsPerMma + static_cast<int>(rank) * (kPairColsPerMma / 2);
+                    if (TM)  // B[N][K]: x = k, y = token; one box of 64 k values x 128 tokens
+                        ptx::tma_load_2d_pair(b_base + (s * NM + m) * BT::kBytes, &p.b_map, j * kTileCols, col0, bar);
+                    else
 #pragma unroll
-                    for (int a = 0; a < BT::kAtoms; a++)
-                        ptx::tma_load_2d_pair(b_base + (s * NM + m) * BT::kBytes + a * BT::kAtomBytes, &p.b_map,
-                                         static_cast<int>(blockIdx.y) * NBLK + m * kPairColsPerMma
-                                             + static_cast<int>(rank) * (kPairColsPerMma / 2) + a * BT::kAtomCols,
-                                         j * kTileCols, bar);
+                        for (int a = 0; a < BT::kAtoms; a++)
+                            ptx::tma_load_2d_pair(b_base + (s * NM + m) * BT::kBytes + a * BT::kAtomBytes, &p.b_map,
+                                                  col0 + a * BT::kAtomCols, j * kTileCols, bar);
+                }
                 if (++j == tiles_k)
                     j = 0;
             }
@@ -321,9 +342,10 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
         ptx::grid_dependency_wait();
         if (lane == 0 && rank == 0) {
             // ------------------------------------------------------------ leader: MMA issue for the pair
-            constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(2 * kTileRows, kPairColsPerMma, false, true);
+            constexpr uint32_t idesc   = ptx::make_idesc_f16_f32(2 * kTileRows, kPairColsPerMma, false, TM ? false : true);
             const uint64_t     a_desc0 = ptx::make_smem_desc(a_base, 16, 1024, ptx::kSwizzle128B);
-            const uint64_t     b_desc0 = ptx::make_smem_desc(b_base, BT::kLeadingBytes, BT::kGroupBytes, BT::kSwizzleMode);
+            const uint64_t     b_desc0 = TM ? ptx::make_smem_desc(b_base, 16, 1024, ptx::kSwizzle128B)
+                                            : ptx::make_smem_desc(b_base, BT::kLeadingBytes, BT::kGroupBytes, BT::kSwizzleMode);
             const uint32_t     partner_done0     = ptx::map_to_cta(done(0), 1);
             const uint32_t     partner_acc_full0 = ptx::map_to_cta(acc_full(0), 1);
             bool ok  = true;
@@ -353,7 +375,7 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                             const uint64_t b_desc = b_desc0 + static_cast<uint64_t>((sb * NM + m) * (BT::kBytes >> 4));
                             ptx::umma_f16_ss_pair(d_tmem + m * kPairColsPerMma,
                                                   a_desc + static_cast<uint64_t>((k * 32) >> 4),
-                                                  b_desc + static_cast<uint64_t>((k * 2 * BT::kGroupBytes) >> 4),
+                                                  b_desc + static_cast<uint64_t>((TM ? k * 32 : k * 2 * BT::kGroupBytes) >> 4),
                                                   idesc,
                                                   k == 0 ? accumulate : 1u);
                         }
@@ -395,8 +417,14 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                 ptx::tmem_ld_wait();
             };
             auto store_c_chunk = [&](int c, const float* v) {
-                uint4* dst = reinterpret_cast<uint4*>(p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
-                                                      + static_cast<size_t>(blockIdx.y) * NBLK + c * CH);
+                if (TM) {
+                    half* dst = c_origin(row_tile, row_in_tile);  // C[n][m]
+#pragma unroll
+                    for (int n = 0; n < CH; n++)
+                        dst[static_cast<size_t>(c * CH + n) * p.m] = __float2half_rn(v[n]);
+                    return;
+                }
+                uint4* dst = reinterpret_cast<uint4*>(c_origin(row_tile, row_in_tile) + c * CH);
 #pragma unroll
                 for (int i = 0; i < CH / 8; i++) {
                     __half2 h0 = __floats2half2_rn(v[8 * i], v[8 * i + 1]);
@@ -479,12 +507,9 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
                         }
                     }
                     else
-                        sum_parked_row<NBLK>(reinterpret_cast<const float4*>(slots) + static_cast<size_t>(first_slot) * (kTileRows * NBLK / 4)
-                                                 + row_in_tile,
-                                             kTileRows * NBLK / 4, g_last - g_first + 1,
-                                             p.C + (static_cast<size_t>(row_tile) * kTileRows + row_in_tile) * p.ld
-                                                 + static_cast<size_t>(blockIdx.y) * NBLK,
-                                             0, 1);
+                        sum_parked_row<NBLK, TM>(reinterpret_cast<const float4*>(slots)
+                                                     + static_cast<size_t>(first_slot) * (kTileRows * NBLK / 4) + row_in_tile,
+                                                 kTileRows * NBLK / 4, g_last - g_first + 1, c_origin(row_tile, row_in_tile), p.m, 0, 1);
                 }
                 l += len;
                 continue;
@@ -510,11 +535,9 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
         for (int quarter = 0; quarter < kEpilogueWarps; quarter++)
             if ((mask >> quarter) & 1) {
                 const int row = quarter * 32 + lane;
-                sum_parked_row<NBLK>(slots4 + static_cast<size_t>(pending->first_slot) * (kTileRows * NBLK / 4) + row,
-                                     kTileRows * NBLK / 4, pending->owners,
-                                     p.C + (static_cast<size_t>(pending->row_tile) * kTileRows + row) * p.ld
-                                         + static_cast<size_t>(blockIdx.y) * NBLK,
-                                     warp, static_cast<int>(blockDim.x) / 32);
+                sum_parked_row<NBLK, TM>(slots4 + static_cast<size_t>(pending->first_slot) * (kTileRows * NBLK / 4) + row,
+                                         kTileRows * NBLK / 4, pending->owners, c_origin(pending->row_tile, row), p.m, warp,
+                                         static_cast<int>(blockDim.x) / 32);
             }
     }
     // Neither block leaves while its partner may still arrive on its barriers or the leader's MMAs may

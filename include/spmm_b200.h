@@ -96,7 +96,11 @@ typedef struct spmm_b200_host_io_item {
 int spmm_b200_spmm_splitk_host_io_batch(void* stream, int count, const spmm_b200_host_io_item* items);
 
 /* The eleven-argument upstream form of SpMM_SplitK_API that the reference's FasterTransformer
- * glue calls (third_party/ft.patch:2822-2846), with token-major layouts: B[N][K], C[N][M]. */
+ * glue calls (third_party/ft.patch:2822-2846), with token-major layouts: B[N][K], C[N][M].
+ * N: 8, 16, 32, 64, and multiples of 64 up to 8192 (the glue's calls with more than 64 tokens,
+ * third_party/ft.patch:523,1454): multiples of 256 with M a multiple of 256 run on pairs of SMs
+ * (B arrives as K-contiguous TMA boxes, the layout the tensor core reads directly), other widths in
+ * column blocks of 64 tokens. */
 int spmm_b200_spmm_splitk_token_major(void*       stream,
                                       const void* Compressed_A,
                                       const int*  TileOffsets,

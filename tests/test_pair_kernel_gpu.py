@@ -91,3 +91,39 @@ def test_rows_not_a_multiple_of_256_stay_on_the_single_block_kernel(sp, oracle, 
     sp.set_pair_kernel(False)
     assert np.array_equal(run_spmm(sp, torch_cuda, words, offsets, B, M, N, K, 2), C)
     assert oracle.tolerance_check(C, oracle.spmm_f64(A, B))[0]
+
+
+TOKEN_MAJOR_CASES = [  # M, K, N, sparsity
+    (512, 1024, 128, 0.8),    # two column blocks of 64 tokens on the single-block kernel
+    (1152, 1024, 192, 0.8),   # M is no multiple of 256: single-block kernel, three column blocks
+    (768, 1152, 256, 0.7),    # pairs of SMs, one MMA per k step
+    (2304, 1152, 512, 0.8),   # pairs of SMs, two MMAs per k step
+    (1536, 640, 768, 0.5),    # three column blocks of 256
+    (2560, 4608, 1024, 0.9),  # two column blocks of 512, split rows and whole rows
+]
+
+
+@pytest.mark.parametrize("case", TOKEN_MAJOR_CASES, ids=["M%d_K%d_N%d_p%g" % c for c in TOKEN_MAJOR_CASES])
+def test_token_major_layout_at_prefill_widths(sp, oracle, torch_cuda, case):
+    """The upstream eleven-argument form (third_party/ft.patch:2822-2846), B[N][K] and C[N][M], beyond 64 tokens."""
+    torch = torch_cuda
+    dev = torch.device("cuda:0")
+    M, K, N, p = case
+    A = sp.synth_fp16((M, K), 5000 + M + N, 0.02, p)
+    B = sp.synth_fp16((K, N), 6000 + M + N, 1.0, 0.0)
+    words, offsets, _ = sp.InitSparseMatrixA_API(A, M, N, K)
+    wd = torch.from_numpy(words.view(np.int32)).to(dev)
+    od = torch.from_numpy(offsets).to(dev)
+    Bt = torch.from_numpy(np.ascontiguousarray(B.T).view(np.int16)).to(dev)          # [N][K]
+    Ct = torch.full((N, M), 0x7E00, dtype=torch.int16, device=dev)                   # [N][M]
+    sk = 8
+    ws = torch.zeros(sp.workspace_bytes(M, N, sk) // 2, dtype=torch.int16, device=dev)
+    assert sp.SpMM_SplitK_API_token_major(None, wd, od, Bt, Ct, M, N, K, ws, sk) == 0
+    torch.cuda.synchronize()
+    assert sp.device_status() == 0
+    C = np.ascontiguousarray(Ct.cpu().numpy().view(np.uint16).T)
+    ok, max_ratio, mean_rel = oracle.tolerance_check(C, oracle.spmm_f64(A, B))
+    assert ok, (max_ratio, mean_rel)
+    if M % 256 == 0 and N % 256 == 0:
+        # on pairs of SMs both layouts use the same partition and accumulate in the same order: same bits
+        assert np.array_equal(C, run_spmm(sp, torch, words, offsets, B, M, N, K, sk))
