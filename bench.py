@@ -153,6 +153,7 @@ class Layer:
             d0 = torch.from_numpy(A.view(np.float16)).to(dev)
             self.dense = [d0] + [d0.clone() for _ in range(dense_copies - 1)]
         self.pair = None      # row-parallel layers, world > 1: fp32 partial rows + the reduction kernel over peer memory
+        self.pair2 = None     # the same partial rows + the two-phase reduction kernel (each rank sums its share of the rows)
         self.fused = None     # the same sum inside the SpMM kernel
         self.result = self.C  # where the layer's final result lies after a step
 
@@ -261,6 +262,8 @@ def run_ours(args):
         for L in some_layers:
             if L.split == "cols":
                 L.pair = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=False)
+                L.pair2 = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=False,
+                                                  two_phase=True)
                 L.fused = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=True)
 
     layers = build(LAYERS, 0, True)
@@ -274,16 +277,19 @@ def run_ours(args):
             if rank == 0:
                 print("peer-memory reduction unavailable:", exc, file=sys.stderr)
         peer_ok = reduce_sum([1.0 if peer_ok else 0.0])[0] == world
-    # "peer": fp32 partial rows, then the library's reduction kernel over peer memory (two launches); "fused": the same
-    # sum inside the SpMM kernel (one launch); "nccl": fp16 results all-reduced by NCCL; "none": no sum (timing only)
-    modes = ["none"] if world == 1 else (["peer", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
+    # "peer": fp32 partial rows, then the library's reduction kernel over peer memory (two launches; every rank pulls all
+    # ranks' rows); "peer2": the two-phase form of that kernel (every rank sums its share of the rows and pushes the
+    # result to all ranks: fewer bytes but one more flag exchange, measured 3-5 us slower per sum on 2 and 4 GPUs);
+    # "fused": the sum inside the SpMM kernel (one launch); "nccl": fp16 results all-reduced by NCCL; "none": no sum
+    # (timing only)
+    modes = ["none"] if world == 1 else (["peer", "peer2", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
     main_mode = modes[0]
 
     def run_layer(L, copy, mode, use):
         """SpMM of layer L (+ the sum over ranks for a layer split by K).  `use`: running count of uses of L, for the
         alternation between its two peer-reduction objects."""
-        if L.split == "cols" and mode in ("fused", "peer"):
-            layer = L.fused if mode == "fused" else L.pair
+        if L.split == "cols" and mode in ("fused", "peer", "peer2"):
+            layer = {"fused": L.fused, "peer": L.pair, "peer2": L.pair2}[mode]
             L.result = layer.forward(L.B, words=L.words[copy % len(L.words)]).view(torch.int16)
         else:
             L.launch(sp, copy)
@@ -468,9 +474,11 @@ def run_ours(args):
         leave(0)
     value = weight_bytes / (ms_per_step * 1e-3) / 1e9
     achieved = algo_bytes / world / (ms_per_step * 1e-3) / 1e9  # per GPU: the roofline is a per-GPU figure
-    launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode == "peer" else 0)
+    launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode in ("peer", "peer2") else 0)
     reduce_note = {"none": "no collective (one GPU)", "fused": "fp32 partials summed inside the SpMM kernel, plain NVLink peer loads",
                    "peer": "fp32 partials summed by the library's reduction kernel, plain NVLink peer loads",
+                   "peer2": "fp32 partials summed by the library's two-phase reduction kernel (each rank sums its share of the "
+                            "rows out of peer memory and stores the result to all ranks over NVLink)",
                    "nccl": "NCCL all-reduce of fp16 results"}[main_mode]
     line = {
         "metric": METRIC,

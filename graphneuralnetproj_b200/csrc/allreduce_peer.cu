@@ -137,6 +137,113 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
     }
 }
 
+
+// Two-phase form for larger worlds (reduce-scatter, then all-gather by remote stores): every rank adds only
+// its own 1 / world of the outputs out of all ranks' fp32 partial results and writes the rounded slice into
+// every rank's result buffer; a second flag exchange tells the peers that the slice has arrived.  Against
+// the one-phase form, which pulls all ranks' complete partial results into every rank (world * count * 4
+// bytes over NVLink per rank), a rank reads count * 4 bytes and writes count * 2: at eight ranks 4.1 MB
+// become 0.7 MB per sum, for one more flag round trip.  Flags: entries [0, world) of a rank's flag array are
+// "partial result of sender s is complete", entries [world, 2 world) "sender s has written its slice here".
+struct TwoPhaseParams {
+    const float4* partial[2][kMaxRanks];  // [epoch parity][rank]: fp32 partial results, count floats each
+    uint32_t*     flags[kMaxRanks];       // 2 * world words per rank
+    uint4*        out[kMaxRanks];         // every rank's result buffer (count halves), mapped here
+    size_t        slice_vectors;          // count / 8 / world: outputs this rank sums, in vectors of eight
+    int           rank, world;
+    uint32_t*     state;                  // [0] epoch of the previous call, [1] blocks finished
+    unsigned long long limit_ns;
+};
+
+__global__ void __launch_bounds__(256) allreduce_two_phase_kernel(const __grid_constant__ TwoPhaseParams p)
+{
+    __shared__ int ok, last;
+    ptx::grid_dependency_wait();  // the SpMM before this kernel in the stream wrote this rank's partial result
+    if (threadIdx.x == 0) {
+        ok   = 1;
+        last = 0;
+    }
+    uint32_t previous;
+    asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.state) : "memory");
+    const uint32_t epoch = previous + 1;
+    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+        __threadfence_system();
+        asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.rank), "r"(epoch) : "memory");
+    }
+    __syncthreads();
+    // bounded wait for `count` flags of this rank's array, starting at entry `first`
+    auto wait_flags = [&](int first) {
+        if (threadIdx.x < p.world) {
+            const uint32_t*          mine  = p.flags[p.rank] + first + threadIdx.x;
+            const unsigned long long start = ptx::global_timer_ns();
+            for (unsigned polls = 0;; polls++) {
+                uint32_t seen;
+                asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(seen) : "l"(mine) : "memory");
+                if (static_cast<int32_t>(seen - epoch) >= 0)
+                    break;
+                if ((polls & 255u) == 255u && ptx::global_timer_ns() - start > p.limit_ns) {
+                    ok = 0;  // a peer never arrived: give up and report
+                    atomicExch(&g_device_status_allreduce, 1);
+                    break;
+                }
+            }
+        }
+        __syncthreads();
+    };
+    wait_flags(0);
+    const float4* const* partial = p.partial[epoch & 1u];
+    const size_t         begin   = p.slice_vectors * p.rank;
+    for (size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x; ok && i < p.slice_vectors;
+         i += static_cast<size_t>(gridDim.x) * blockDim.x) {
+        // all ranks' loads first, then the sums in rank order: one NVLink round trip
+        float4 v[kMaxRanks][2];
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < p.world) {
+                const float4* src = partial[r] + 2 * (begin + i);
+                v[r][0]           = __ldcv(src);
+                v[r][1]           = __ldcv(src + 1);
+            }
+        float sum[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < p.world) {
+                sum[0] += v[r][0].x, sum[1] += v[r][0].y, sum[2] += v[r][0].z, sum[3] += v[r][0].w;
+                sum[4] += v[r][1].x, sum[5] += v[r][1].y, sum[6] += v[r][1].z, sum[7] += v[r][1].w;
+            }
+        uint4    o;
+        __half2* oh = reinterpret_cast<__half2*>(&o);
+#pragma unroll
+        for (int k = 0; k < 4; k++)
+            oh[k] = __floats2half2_rn(sum[2 * k], sum[2 * k + 1]);
+#pragma unroll
+        for (int r = 0; r < kMaxRanks; r++)
+            if (r < p.world)
+                p.out[r][begin + i] = o;  // every rank gets the same bits
+    }
+    // The last block of this rank to finish tells every peer that the slice has arrived (the block's stores are
+    // ordered before thread 0's system-scope fence by the barrier), then waits for the peers' slices: when
+    // this kernel completes, this rank's result buffer is complete.
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence_system();
+        if (atomicAdd(p.state + 1, 1u) == gridDim.x - 1) {
+            p.state[1] = 0;
+            last       = 1;
+        }
+    }
+    __syncthreads();
+    if (last) {
+        if (threadIdx.x < p.world)
+            asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.world + p.rank), "r"(epoch) : "memory");
+        wait_flags(p.world);
+        if (threadIdx.x == 0) {
+            __threadfence();
+            p.state[0] = epoch;
+        }
+    }
+}
+
 }  // namespace spmm_b200
 
 namespace spmm_b200 {
@@ -245,4 +352,50 @@ extern "C" int spmm_b200_allreduce_partials_f32(void*              stream,
         return static_cast<int>(cudaErrorInvalidValue);
     return spmm_b200::launch_allreduce(stream, partial_buffers, flag_arrays, rank, world, out, count, 0,
                                        static_cast<uint32_t*>(state), limit_ms, true);
+}
+
+extern "C" int spmm_b200_allreduce_partials_f32_two_phase(void*              stream,
+                                                          const void* const* partial_buffers,
+                                                          void* const*       flag_arrays,
+                                                          void* const*       out_buffers,
+                                                          int                rank,
+                                                          int                world,
+                                                          size_t             count,
+                                                          void*              state,
+                                                          unsigned           limit_ms)
+{
+    using namespace spmm_b200;
+    if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || count == 0 || count % (8 * static_cast<size_t>(world)) != 0
+        || !partial_buffers || !flag_arrays || !out_buffers || !state || (reinterpret_cast<uintptr_t>(state) & 3u))
+        return static_cast<int>(cudaErrorInvalidValue);
+    TwoPhaseParams p;
+    for (int r = 0; r < world; r++) {
+        for (int parity = 0; parity < 2; parity++) {
+            const void* buffer = partial_buffers[parity * world + r];
+            if (!buffer || (reinterpret_cast<uintptr_t>(buffer) & 15u))
+                return static_cast<int>(cudaErrorInvalidValue);
+            p.partial[parity][r] = static_cast<const float4*>(buffer);
+        }
+        if (!flag_arrays[r] || !out_buffers[r] || (reinterpret_cast<uintptr_t>(out_buffers[r]) & 15u))
+            return static_cast<int>(cudaErrorInvalidValue);
+        p.flags[r] = static_cast<uint32_t*>(flag_arrays[r]);
+        p.out[r]   = static_cast<uint4*>(out_buffers[r]);
+    }
+    p.slice_vectors = count / 8 / world;
+    p.rank          = rank;
+    p.world         = world;
+    p.state         = static_cast<uint32_t*>(state);
+    p.limit_ns      = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
+    const int blocks = static_cast<int>(p.slice_vectors < 256 * 148 ? (p.slice_vectors + 255) / 256 : 148);
+    cudaLaunchConfig_t config = {};
+    config.gridDim            = dim3(blocks > 0 ? blocks : 1);
+    config.blockDim           = dim3(256);
+    config.stream             = static_cast<cudaStream_t>(stream);
+    cudaLaunchAttribute attr[1];
+    attr[0].id                                         = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    config.attrs                                       = attr;
+    config.numAttrs                                    = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, allreduce_two_phase_kernel, p);
+    return static_cast<int>(e != cudaSuccess ? e : cudaGetLastError());
 }

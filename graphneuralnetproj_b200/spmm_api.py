@@ -76,6 +76,11 @@ def _load():
                                                      ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int,
                                                      ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_uint]
     lib.spmm_b200_allreduce_partials_f32.restype = ctypes.c_int
+    lib.spmm_b200_allreduce_partials_f32_two_phase.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
+                                                               ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
+                                                               ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p,
+                                                               ctypes.c_uint]
+    lib.spmm_b200_allreduce_partials_f32_two_phase.restype = ctypes.c_int
     lib.spmm_b200_allreduce_status.argtypes = [ctypes.c_int]
     lib.spmm_b200_allreduce_status.restype = ctypes.c_int
     lib.spmm_b200_set_weights_constant.argtypes = [ctypes.c_int]

@@ -166,7 +166,7 @@ class FusedRowParallelSpMM:
     symmetric flag array and the epoch state.  Every rank must construct it and call `forward` the same number
     of times.  With no process group (or a world of one) it runs stand-alone on one GPU."""
 
-    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None, fused=True):
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None, fused=True, two_phase=False):
         import ctypes
 
         import torch
@@ -177,6 +177,9 @@ class FusedRowParallelSpMM:
         self.words, self.offsets = words_dev, offsets_dev
         self.M, self.N, self.K, self.split_k = M, N, K_shard, split_k
         self.fused = fused
+        # two_phase (with fused=False): spmm_b200_allreduce_partials_f32_two_phase -- every rank sums its share of
+        # the rows and writes the result into all ranks' (symmetric) result buffers
+        self.two_phase = bool(two_phase) and not fused
         dev = words_dev.device
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.rank = dist.get_rank(group) if distributed else 0
@@ -194,6 +197,14 @@ class FusedRowParallelSpMM:
             handles = [symm_mem.rendezvous(b, group) for b in self.partials]
             flag_handle = symm_mem.rendezvous(self.flags, group)
             self._handles = handles + [flag_handle]  # keep the mappings alive
+            if self.two_phase:
+                if (M * N) % (8 * self.world) != 0:
+                    raise ValueError("M * N must be a multiple of 8 * world for the two-phase sum")
+                self.C = symm_mem.empty((M, N), dtype=torch.float16, device=dev)
+                self.C.zero_()
+                out_handle = symm_mem.rendezvous(self.C, group)
+                self._handles.append(out_handle)
+                self._out_ptrs = ptr_array(*[int(p) for p in out_handle.buffer_ptrs])
             self._partial_ptrs = (ctypes.c_void_p * (2 * self.world))(*[int(p) for h in handles for p in h.buffer_ptrs])
             self._flag_ptrs = ptr_array(*[int(p) for p in flag_handle.buffer_ptrs])
         else:
@@ -202,7 +213,9 @@ class FusedRowParallelSpMM:
             self._partial_ptrs = (ctypes.c_void_p * 2)(self.partials[0].data_ptr(), self.partials[1].data_ptr())
             self._flag_ptrs = ptr_array(self.flags.data_ptr())
         self.state = torch.zeros(2, dtype=torch.int32, device=dev)
-        self.C = torch.zeros((M, N), dtype=torch.float16, device=dev)
+        if not (distributed and self.two_phase):
+            self.C = torch.zeros((M, N), dtype=torch.float16, device=dev)
+            self._out_ptrs = ptr_array(self.C.data_ptr()) if not distributed else None
         self.workspace = torch.zeros(spmm_api.workspace_bytes(M, N, split_k) // 2, dtype=torch.int16, device=dev)
         torch.cuda.synchronize(dev)
         if distributed:
@@ -224,7 +237,13 @@ class FusedRowParallelSpMM:
             ctypes.c_void_p(self.state.data_ptr()), limit_ms, 0 if self.fused else 1)
         if rc != 0:
             raise RuntimeError("spmm_b200_spmm_row_parallel failed with cudaError %d" % rc)
-        if not self.fused:
+        if self.two_phase:
+            rc = self._api.LIB.spmm_b200_allreduce_partials_f32_two_phase(
+                ctypes.c_void_p(stream.cuda_stream), self._partial_ptrs, self._flag_ptrs, self._out_ptrs, self.rank, self.world,
+                self.M * self.N, ctypes.c_void_p(self.state.data_ptr()), limit_ms)
+            if rc != 0:
+                raise RuntimeError("spmm_b200_allreduce_partials_f32_two_phase failed with cudaError %d" % rc)
+        elif not self.fused:
             rc = self._api.LIB.spmm_b200_allreduce_partials_f32(
                 ctypes.c_void_p(stream.cuda_stream), self._partial_ptrs, self._flag_ptrs, self.rank, self.world,
                 ctypes.c_void_p(self.C.data_ptr()), self.M * self.N, ctypes.c_void_p(self.state.data_ptr()), limit_ms)

@@ -53,6 +53,19 @@ def test_replayable_reduction_argument_checks(sp):
     assert lib.spmm_b200_allreduce_partials_replayable(None, two, two, 0, 2, out, 60, ctypes.c_void_p(16), 0) == 1
 
 
+def test_two_phase_reduction_argument_checks(sp):
+    lib = sp.spmm_api.LIB
+    four = (ctypes.c_void_p * 4)(16, 32, 48, 64)
+    two = (ctypes.c_void_p * 2)(16, 32)
+    state = ctypes.c_void_p(16)
+    f = lib.spmm_b200_allreduce_partials_f32_two_phase
+    assert f(None, four, two, two, 0, 2, 64, None, 0) == 1                 # no state
+    assert f(None, four, two, two, 0, 2, 24, state, 0) == 1                # count is no multiple of 8 * world
+    assert f(None, four, two, None, 0, 2, 64, state, 0) == 1               # no result buffers
+    assert f(None, four, two, two, 2, 2, 64, state, 0) == 1                # rank outside the world
+    assert f(None, four, two, (ctypes.c_void_p * 2)(16, 40), 0, 2, 64, state, 0) == 1  # misaligned result buffer
+
+
 def test_weights_constant_switch(sp):
     before = sp.set_weights_constant(True)
     assert sp.set_weights_constant(False) is True
