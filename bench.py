@@ -154,6 +154,7 @@ class Layer:
             self.dense = [d0] + [d0.clone() for _ in range(dense_copies - 1)]
         self.pair = None      # row-parallel layers, world > 1: fp32 partial rows + the reduction kernel over peer memory
         self.pair2 = None     # the same partial rows + the two-phase reduction kernel (each rank sums its share of the rows)
+        self.paira = None     # partial rows announced to the peers by the SpMM's last block + the reduction kernel
         self.fused = None     # the same sum inside the SpMM kernel
         self.result = self.C  # where the layer's final result lies after a step
 
@@ -262,6 +263,8 @@ def run_ours(args):
         for L in some_layers:
             if L.split == "cols":
                 L.pair = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=False)
+                L.paira = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=False,
+                                                  announce=True)
                 L.pair2 = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=False,
                                                   two_phase=True)
                 L.fused = tp.FusedRowParallelSpMM(L.words[0], L.offsets, L.M, N, L.K, split_k=L.split_k, fused=True)
@@ -282,14 +285,16 @@ def run_ours(args):
     # result to all ranks: fewer bytes but one more flag exchange, measured 3-5 us slower per sum on 2 and 4 GPUs);
     # "fused": the sum inside the SpMM kernel (one launch); "nccl": fp16 results all-reduced by NCCL; "none": no sum
     # (timing only)
-    modes = ["none"] if world == 1 else (["peer", "peer2", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
+    # "peera": as "peer", but the SpMM's last block flags the partial rows to the peers, so the exchange of flags
+    # overlaps the launch of the reduction kernel
+    modes = ["none"] if world == 1 else (["peer", "peera", "peer2", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
     main_mode = modes[0]
 
     def run_layer(L, copy, mode, use):
         """SpMM of layer L (+ the sum over ranks for a layer split by K).  `use`: running count of uses of L, for the
         alternation between its two peer-reduction objects."""
-        if L.split == "cols" and mode in ("fused", "peer", "peer2"):
-            layer = {"fused": L.fused, "peer": L.pair, "peer2": L.pair2}[mode]
+        if L.split == "cols" and mode in ("fused", "peer", "peera", "peer2"):
+            layer = {"fused": L.fused, "peer": L.pair, "peera": L.paira, "peer2": L.pair2}[mode]
             L.result = layer.forward(L.B, words=L.words[copy % len(L.words)]).view(torch.int16)
         else:
             L.launch(sp, copy)
@@ -474,9 +479,11 @@ def run_ours(args):
         leave(0)
     value = weight_bytes / (ms_per_step * 1e-3) / 1e9
     achieved = algo_bytes / world / (ms_per_step * 1e-3) / 1e9  # per GPU: the roofline is a per-GPU figure
-    launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode in ("peer", "peer2") else 0)
+    launches_per_step = len(layers) + (sum(1 for L in layers if L.split == "cols") if main_mode in ("peer", "peera", "peer2") else 0)
     reduce_note = {"none": "no collective (one GPU)", "fused": "fp32 partials summed inside the SpMM kernel, plain NVLink peer loads",
                    "peer": "fp32 partials summed by the library's reduction kernel, plain NVLink peer loads",
+                   "peera": "fp32 partials flagged to the peers by the SpMM's last block and summed by the library's reduction "
+                            "kernel, plain NVLink peer loads",
                    "peer2": "fp32 partials summed by the library's two-phase reduction kernel (each rank sums its share of the "
                             "rows out of peer memory and stores the result to all ranks over NVLink)",
                    "nccl": "NCCL all-reduce of fp16 results"}[main_mode]

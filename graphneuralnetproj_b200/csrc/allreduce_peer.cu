@@ -42,6 +42,7 @@ struct AllReduceParams {
     int          rank, world;
     uint32_t     epoch;               // this call's epoch when `state` is null
     uint32_t*    state;               // or: state[0] = epoch of the previous call, state[1] = blocks finished
+    int          announced;           // 1: the kernel that wrote the partial result has told the peers already
     unsigned long long limit_ns;
 };
 
@@ -61,7 +62,7 @@ __global__ void __launch_bounds__(256) allreduce_partials_kernel(const __grid_co
         asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.state) : "memory");
         epoch = previous + 1;
     }
-    if (blockIdx.x == 0 && threadIdx.x < p.world) {
+    if (blockIdx.x == 0 && threadIdx.x < p.world && !p.announced) {
         // this rank's partial result is complete and visible: tell peer threadIdx.x
         __threadfence_system();
         asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p.flags[threadIdx.x] + p.rank), "r"(epoch) : "memory");
@@ -249,7 +250,7 @@ __global__ void __launch_bounds__(256) allreduce_two_phase_kernel(const __grid_c
 namespace spmm_b200 {
 namespace {
 int launch_allreduce(void* stream, const void* const* partial_buffers, void* const* flag_arrays, int rank, int world, void* out,
-                     size_t count, uint32_t epoch, uint32_t* state, unsigned limit_ms, bool f32 = false)
+                     size_t count, uint32_t epoch, uint32_t* state, unsigned limit_ms, bool f32 = false, bool announced = false)
 {
     if (world < 1 || world > kMaxRanks || rank < 0 || rank >= world || count % 8 != 0 || !out || !partial_buffers
         || !flag_arrays || (epoch == 0 && state == nullptr) || (f32 && state == nullptr))
@@ -274,7 +275,8 @@ int launch_allreduce(void* stream, const void* const* partial_buffers, void* con
     p.rank     = rank;
     p.world    = world;
     p.epoch    = epoch;
-    p.state    = state;
+    p.state     = state;
+    p.announced = announced ? 1 : 0;
     p.limit_ns = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
     const int blocks = static_cast<int>(p.vectors < 256 * 148 ? (p.vectors + 255) / 256 : 148);
     cudaLaunchConfig_t config = {};
@@ -352,6 +354,22 @@ extern "C" int spmm_b200_allreduce_partials_f32(void*              stream,
         return static_cast<int>(cudaErrorInvalidValue);
     return spmm_b200::launch_allreduce(stream, partial_buffers, flag_arrays, rank, world, out, count, 0,
                                        static_cast<uint32_t*>(state), limit_ms, true);
+}
+
+extern "C" int spmm_b200_allreduce_partials_f32_announced(void*              stream,
+                                                          const void* const* partial_buffers,
+                                                          void* const*       flag_arrays,
+                                                          int                rank,
+                                                          int                world,
+                                                          void*              out,
+                                                          size_t             count,
+                                                          void*              state,
+                                                          unsigned           limit_ms)
+{
+    if (state == nullptr || (reinterpret_cast<uintptr_t>(state) & 3u))
+        return static_cast<int>(cudaErrorInvalidValue);
+    return spmm_b200::launch_allreduce(stream, partial_buffers, flag_arrays, rank, world, out, count, 0,
+                                       static_cast<uint32_t*>(state), limit_ms, true, true);
 }
 
 extern "C" int spmm_b200_allreduce_partials_f32_two_phase(void*              stream,

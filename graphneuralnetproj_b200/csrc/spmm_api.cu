@@ -925,7 +925,7 @@ int spmm_b200_spmm_row_parallel(void*        stream,
     peer.state    = static_cast<uint32_t*>(state);
     peer.rank     = rank;
     peer.world    = world;
-    peer.partial_only = partial_only ? 1 : 0;
+    peer.partial_only = partial_only == 2 ? 2 : (partial_only ? 1 : 0);
     peer.limit_ns = static_cast<unsigned long long>(limit_ms ? limit_ms : 2000u) * 1000000ull;
     return static_cast<int>(spmm_tiled_csl(static_cast<cudaStream_t>(stream), static_cast<const uint4*>(Compressed_A), TileOffsets,
                                            static_cast<const half*>(B), static_cast<half*>(C), M_Global, N_Global, K_Global,

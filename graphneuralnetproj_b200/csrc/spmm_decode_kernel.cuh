@@ -90,6 +90,9 @@ struct PeerSumParams {
     int       rank = 0, world = 0;              // world == 0: no sum over ranks
     // 1: only write this rank's fp32 partial rows (buffer of parity (state[0] + 1) & 1); the flags, the sum and
     // the advance of the epoch are left to the reduction kernel launched next in the stream
+    // 2: as 1, and the last block of this kernel to finish tells every rank that the partial rows are complete (entry
+    //    [rank] of every rank's flag array gets the call's epoch), so that the exchange of flags travels while the
+    //    reduction kernel is being launched; that kernel then only waits for the flags
     int       partial_only = 0;
     unsigned long long limit_ns = 0;
 };
@@ -830,6 +833,20 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             p.peer.state[1] = 0;
             __threadfence();
             p.peer.state[0] = previous + 1;
+        }
+    }
+    if (threadIdx.x == 0 && p.peer.world > 0 && p.peer.partial_only == 2) {
+        // Partial rows with the announcement: every block's rows are ordered before its count, the last block to count
+        // orders all of them before the flags with one system-scope fence.  state[1] is back at zero before the
+        // reduction kernel, which waits for this kernel, uses it.
+        uint32_t previous;
+        asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.peer.state) : "memory");
+        __threadfence();
+        if (atomicAdd(p.peer.state + 1, 1u) == gridDim.x * gridDim.y - 1) {
+            p.peer.state[1] = 0;
+            __threadfence_system();
+            for (int r = 0; r < p.peer.world; r++)
+                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.peer.flags[r] + p.peer.rank), "r"(previous + 1) : "memory");
         }
     }
     if (warp == kFirstMmaWarp) {

@@ -76,6 +76,8 @@ def _load():
                                                      ctypes.POINTER(ctypes.c_void_p), ctypes.c_int, ctypes.c_int,
                                                      ctypes.c_void_p, ctypes.c_size_t, ctypes.c_void_p, ctypes.c_uint]
     lib.spmm_b200_allreduce_partials_f32.restype = ctypes.c_int
+    lib.spmm_b200_allreduce_partials_f32_announced.argtypes = lib.spmm_b200_allreduce_partials_f32.argtypes
+    lib.spmm_b200_allreduce_partials_f32_announced.restype = ctypes.c_int
     lib.spmm_b200_allreduce_partials_f32_two_phase.argtypes = [ctypes.c_void_p, ctypes.POINTER(ctypes.c_void_p),
                                                                ctypes.POINTER(ctypes.c_void_p), ctypes.POINTER(ctypes.c_void_p),
                                                                ctypes.c_int, ctypes.c_int, ctypes.c_size_t, ctypes.c_void_p,

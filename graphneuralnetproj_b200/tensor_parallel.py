@@ -166,7 +166,7 @@ class FusedRowParallelSpMM:
     symmetric flag array and the epoch state.  Every rank must construct it and call `forward` the same number
     of times.  With no process group (or a world of one) it runs stand-alone on one GPU."""
 
-    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None, fused=True, two_phase=False):
+    def __init__(self, words_dev, offsets_dev, M, N, K_shard, split_k=8, group=None, fused=True, two_phase=False, announce=False):
         import ctypes
 
         import torch
@@ -180,6 +180,9 @@ class FusedRowParallelSpMM:
         # two_phase (with fused=False): spmm_b200_allreduce_partials_f32_two_phase -- every rank sums its share of
         # the rows and writes the result into all ranks' (symmetric) result buffers
         self.two_phase = bool(two_phase) and not fused
+        # announce (with fused=False, two_phase=False): the SpMM's last block flags the partial rows to the peers
+        # (partial_only = 2) and spmm_b200_allreduce_partials_f32_announced only waits and adds
+        self.announce = bool(announce) and not fused and not two_phase
         dev = words_dev.device
         distributed = dist.is_available() and dist.is_initialized() and dist.get_world_size(group) > 1
         self.rank = dist.get_rank(group) if distributed else 0
@@ -234,7 +237,7 @@ class FusedRowParallelSpMM:
             ctypes.c_void_p(stream.cuda_stream), ctypes.c_void_p(words.data_ptr()), ctypes.c_void_p(self.offsets.data_ptr()),
             ctypes.c_void_p(B_shard_dev.data_ptr()), ctypes.c_void_p(self.C.data_ptr()), self.M, self.N, self.K,
             ctypes.c_void_p(self.workspace.data_ptr()), self.split_k, self._partial_ptrs, self._flag_ptrs, self.rank, self.world,
-            ctypes.c_void_p(self.state.data_ptr()), limit_ms, 0 if self.fused else 1)
+            ctypes.c_void_p(self.state.data_ptr()), limit_ms, 0 if self.fused else (2 if self.announce else 1))
         if rc != 0:
             raise RuntimeError("spmm_b200_spmm_row_parallel failed with cudaError %d" % rc)
         if self.two_phase:
@@ -244,7 +247,9 @@ class FusedRowParallelSpMM:
             if rc != 0:
                 raise RuntimeError("spmm_b200_allreduce_partials_f32_two_phase failed with cudaError %d" % rc)
         elif not self.fused:
-            rc = self._api.LIB.spmm_b200_allreduce_partials_f32(
+            reduce = self._api.LIB.spmm_b200_allreduce_partials_f32_announced if self.announce \
+                else self._api.LIB.spmm_b200_allreduce_partials_f32
+            rc = reduce(
                 ctypes.c_void_p(stream.cuda_stream), self._partial_ptrs, self._flag_ptrs, self.rank, self.world,
                 ctypes.c_void_p(self.C.data_ptr()), self.M * self.N, ctypes.c_void_p(self.state.data_ptr()), limit_ms)
             if rc != 0:

@@ -192,7 +192,9 @@ int spmm_b200_allreduce_partials_replayable(void*              stream,
  *   partial_only     0: as described.  1: the kernel only writes this rank's fp32 partial rows (into the
  *                    buffer of the coming epoch's parity) and neither flags, sums nor advances the epoch:
  *                    spmm_b200_allreduce_partials_f32 on the same buffers, flag arrays and state, launched
- *                    next in the stream, does that (C is then not written by this call).  Measured on two
+ *                    next in the stream, does that (C is then not written by this call).
+ *                    2: as 1, and the last block to finish also tells every rank that the partial rows
+ *                    are complete; spmm_b200_allreduce_partials_f32_announced follows.  Measured on two
  *                    to eight B200s the two-launch form is the faster one: a system-scope fence at the
  *                    end of a kernel that keeps the memory system busy costs more than a launch.
  * world 1..8 (1 degenerates to a copy through the partial buffer); every rank must make the matching
@@ -229,6 +231,21 @@ int spmm_b200_allreduce_partials_f32(void*              stream,
                                      size_t             count,
                                      void*              state,
                                      unsigned           limit_ms);
+
+/* The sum over ranks after spmm_b200_spmm_row_parallel(..., partial_only = 2): that SpMM's last block has
+ * already told every rank that this rank's partial rows are complete, so this kernel only waits for the
+ * peers' flags, adds and writes (the flag exchange travels while this kernel is being launched).
+ * Arguments as for spmm_b200_allreduce_partials_f32; must follow a partial_only = 2 product on the same
+ * buffers, flag arrays and state. */
+int spmm_b200_allreduce_partials_f32_announced(void*              stream,
+                                               const void* const* partial_buffers,
+                                               void* const*       flag_arrays,
+                                               int                rank,
+                                               int                world,
+                                               void*              out,
+                                               size_t             count,
+                                               void*              state,
+                                               unsigned           limit_ms);
 
 /* The same sum in two phases, for larger worlds: every rank adds only its own 1 / world of the outputs
  * out of all ranks' fp32 partial results and writes the rounded slice into every rank's result buffer

@@ -106,13 +106,13 @@ else:
                     for out in outs:
                         assert np.array_equal(out.cpu().numpy().view(np.uint16), total), replay
             assert sp.spmm_api.LIB.spmm_b200_allreduce_status(0) == 0
-        if mode in ("row_fused", "row_two_launches", "row_two_phase"):
+        if mode in ("row_fused", "row_two_launches", "row_two_phase", "row_announced"):
             # fp32 partial rows summed out of peer memory, inside the SpMM kernel or by the reduction kernel
             # launched after it: un-captured calls, then a captured pair replayed; one rounding, so the result
             # is at least as close to the fp64 product as the all-reduced fp16 results
             # (row_two_phase: every rank sums its half of the rows and stores the result into both ranks' buffers)
             fused = tp.FusedRowParallelSpMM(layer.words, layer.offsets, M, N, k, fused=(mode == "row_fused"),
-                                            two_phase=(mode == "row_two_phase"))
+                                            two_phase=(mode == "row_two_phase"), announce=(mode == "row_announced"))
             for call in range(3):
                 fused.C.fill_(float("nan"))
                 out = fused.forward(Bd)
@@ -164,7 +164,7 @@ def test_two_gloo_ranks_on_cpu(mode):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("mode", ["column", "row", "row_peer", "row_peer_graph", "row_fused", "row_two_launches", "row_two_phase"])
+@pytest.mark.parametrize("mode", ["column", "row", "row_peer", "row_peer_graph", "row_fused", "row_two_launches", "row_two_phase", "row_announced"])
 def test_two_nccl_ranks_on_gpus(mode):
     import torch
     if torch.cuda.device_count() < 2:
