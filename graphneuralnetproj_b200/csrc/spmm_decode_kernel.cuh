@@ -75,18 +75,20 @@ constexpr int kMaxPeers = 8;  // ranks of a row-parallel (split by K) layer whos
 
 // Sum over the ranks of a layer split by K, folded into the SpMM's epilogue (no counterpart in the
 // reference, which is single-GPU; its FasterTransformer glue all-reduces with NCCL after the product).
-// Every rank writes its finished rows, still in fp32, to its own partial buffer instead of C, tells every
-// peer row of tiles by row of tiles (one flag per quarter of a row of tiles and sender, carrying the
-// call's epoch), and once a block has finished its own tiles it takes rows of tiles in turn, waits for
-// all ranks' flags, adds the ranks' partial rows in rank order out of the peers' memory (plain loads
-// over NVLink) and rounds once to fp16.  Epochs only grow, so nothing is reset; the partial buffers
-// alternate with the epoch's parity, so a fast rank's next product never overwrites what a slow peer is
-// still reading.  fp32 partials because fp16 ones put the mean relative error of the sum right at the
-// 1e-3 acceptance gate (entries much smaller than their partial sums).
+// Every rank writes its finished rows, still in fp32, to its own partial buffer instead of C.  When all
+// blocks of a rank have written theirs, the last of them tells every rank (one flag per sender, carrying
+// the call's epoch, after one system-scope fence); the blocks then take rows of tiles in turn, wait for
+// all ranks' flags, add the ranks' partial rows in rank order out of the peers' memory (plain loads over
+// NVLink) and round once to fp16.  Epochs only grow, so nothing is reset; the partial buffers alternate
+// with the epoch's parity, so a fast rank's next product never overwrites what a slow peer is still
+// reading.  fp32 partials because fp16 ones put the mean relative error of the sum right at the 1e-3
+// acceptance gate (entries much smaller than their partial sums).  (An earlier form flagged every
+// quarter of a row of tiles as it was finished, to overlap the sums with the product: all rows finish
+// at the end of a balanced persistent kernel, so nothing overlapped and the fences cost 8-16 us.)
 struct PeerSumParams {
     float*    partial[2][kMaxPeers] = {};  // [epoch parity][rank]: that rank's partial result, fp32 [M][N], mapped here
-    uint32_t* flags[kMaxPeers]      = {};  // flags[r]: rank r's flag array, (M / 128) * 4 * world words
-    uint32_t* state                 = nullptr;  // this rank's: [0] epoch of the previous call, [1] blocks finished
+    uint32_t* flags[kMaxPeers]      = {};  // flags[r]: rank r's flag array, one word per sender
+    uint32_t* state                 = nullptr;  // this rank's: [0] epoch of the previous call, [1] block counter
     int       rank = 0, world = 0;              // world == 0: no sum over ranks
     // 1: only write this rank's fp32 partial rows (buffer of parity (state[0] + 1) & 1); the flags, the sum and
     // the advance of the epoch are left to the reduction kernel launched next in the stream
@@ -559,21 +561,6 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             epoch   = previous + 1;  // every earlier launch on this state has completed (stream order)
             c32_out = p.peer.partial[epoch & 1][p.peer.rank];
         }
-        // Tells every rank that this quarter (warp) of row of tiles `row_tile` is complete in c32_out.  One
-        // system-scope fence per warp, by one lane, after the warp's stores have been ordered before it by the
-        // warp barrier: a fence in every lane made the announcement take about 16 us at the end of a launch.
-        auto announce_rows = [&](int row_tile) {
-            __syncwarp();
-            if (lane == 0)
-                asm volatile("fence.acq_rel.sys;" ::: "memory");
-            __syncwarp();
-            if (lane < p.peer.world)
-                asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(
-                                 p.peer.flags[lane] + (static_cast<size_t>(row_tile) * kEpilogueWarps + warp) * p.peer.world
-                                 + p.peer.rank),
-                             "r"(epoch)
-                             : "memory");
-        };
 #pragma unroll 1
         for (int l = 0; l < num_tiles; ++seg) {
             const int  t0       = tile_begin + l;
@@ -667,8 +654,6 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     load_chunk(c, v);
                     store_c_chunk(c, v);
                 }
-                if (peer_sum && !p.peer.partial_only)
-                    announce_rows(row_tile);
             }
             else {
                 // Park the partial row, count arrivals, let the last arriver sum in owner order.
@@ -752,8 +737,6 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                         }
                         store_c_chunk(c, sum);
                     }
-                    if (peer_sum && !p.peer.partial_only)
-                        announce_rows(row_tile);
                 }
             }
             // only now may the MMA warps overwrite this accumulator set
@@ -765,13 +748,27 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
             l += len;
         }
         if (peer_sum && !p.peer.partial_only && blockIdx.y == 0) {
-            // Own tiles done: take rows of tiles in turn, wait for every rank's quarter, add in rank order.
+            // Own tiles done.  When the four epilogue warps of every block of this rank have written their rows, the
+            // last block to count itself tells every rank (one system-scope fence for the whole rank: fences per warp
+            // and row of tiles at the end of a kernel that keeps the memory system busy cost far more).  Then the
+            // blocks take rows of tiles in turn, wait for all ranks' flags -- their own rank's included -- and add
+            // the partial rows in rank order.
+            asm volatile("bar.sync 15, 128;" ::: "memory");
+            if (warp == 0 && lane == 0) {
+                // state[1]: low half counts the blocks whose rows are written, high half the blocks that have left
+                // (a block without rows to add leaves while others still write, so the two counts interleave)
+                __threadfence();
+                if ((atomicAdd(p.peer.state + 1, 1u) & 0xffffu) == gridDim.x * gridDim.y - 1) {
+                    __threadfence_system();
+                    for (int r = 0; r < p.peer.world; r++)
+                        asm volatile("st.relaxed.sys.global.u32 [%0], %1;" ::"l"(p.peer.flags[r] + p.peer.rank), "r"(epoch) : "memory");
+                }
+            }
             const int      tiles_m = p.m / kTileRows;
             float* const* parts = p.peer.partial[epoch & 1];
-#pragma unroll 1
-            for (int rt = cta; rt < tiles_m && *abort_word == 0; rt += gridDim.x) {
+            if (cta < tiles_m) {
                 if (lane < p.peer.world) {
-                    const uint32_t* flag = p.peer.flags[p.peer.rank] + (static_cast<size_t>(rt) * kEpilogueWarps + warp) * p.peer.world + lane;
+                    const uint32_t* flag  = p.peer.flags[p.peer.rank] + lane;
                     const uint64_t  start = ptx::global_timer_ns();
 #pragma unroll 1
                     for (uint32_t polls = 0;; polls++) {
@@ -786,8 +783,9 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
                     }
                 }
                 __syncwarp();
-                if (*abort_word != 0)
-                    break;
+            }
+#pragma unroll 1
+            for (int rt = cta; rt < tiles_m && *abort_word == 0; rt += gridDim.x) {
                 const size_t row = static_cast<size_t>(rt) * kTileRows + row_in_tile;
 #pragma unroll 1
                 for (int c = 0; c < N / 8; c++) {
@@ -829,7 +827,8 @@ spmm_decode_kernel(const __grid_constant__ DecodeParams p)
         uint32_t previous;
         asm volatile("ld.volatile.global.u32 %0, [%1];" : "=r"(previous) : "l"(p.peer.state) : "memory");
         __threadfence();
-        if (atomicAdd(p.peer.state + 1, 1u) == gridDim.x * gridDim.y - 1) {
+        // (the low half of state[1] counted the blocks when their rows were written, see the epilogue)
+        if ((atomicAdd(p.peer.state + 1, 0x10000u) >> 16) == gridDim.x * gridDim.y - 1) {
             p.peer.state[1] = 0;
             __threadfence();
             p.peer.state[0] = previous + 1;

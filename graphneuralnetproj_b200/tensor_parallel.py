@@ -161,8 +161,8 @@ class FusedRowParallelSpMM:
     """One rank's part of a row-parallel layer with fp32 partial results summed over the ranks out of peer
     memory (spmm_b200_spmm_row_parallel): no collective library, one rounding, replayable from a CUDA graph.
     `fused=True`: the sum is folded into the SpMM kernel (one launch per call); `fused=False`: the SpMM only
-    writes its fp32 partial rows and spmm_b200_allreduce_partials_f32 follows as a second launch (the faster
-    form on B200: see include/spmm_b200.h).  Holds the symmetric partial buffers (two, used alternately), the
+    writes its fp32 partial rows and spmm_b200_allreduce_partials_f32 follows as a second launch (as fast,
+    see include/spmm_b200.h).  Holds the symmetric partial buffers (two, used alternately), the
     symmetric flag array and the epoch state.  Every rank must construct it and call `forward` the same number
     of times.  With no process group (or a world of one) it runs stand-alone on one GPU."""
 

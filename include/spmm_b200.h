@@ -176,13 +176,13 @@ int spmm_b200_allreduce_partials_replayable(void*              stream,
  * layer with the sum over the ranks folded into the kernel: no second launch and no collective library
  * on the critical path.  No counterpart in the reference (single-GPU; FasterTransformer all-reduces
  * after the product, third_party/ft.patch:2822-2846 is followed by its NCCL call).  Every rank writes
- * its finished rows into its own partial buffer, flags them to all ranks row of tiles by row of tiles,
- * and the thread blocks that run out of tiles add the ranks' partial rows in rank order out of the
- * peers' memory (plain loads over NVLink, no multimem) into C; every rank ends up with the same bits.
+ * its finished rows into its own partial buffer; the last of its thread blocks to do so flags them to
+ * all ranks, and the thread blocks then add the ranks' partial rows in rank order out of the peers'
+ * memory (plain loads over NVLink, no multimem) into C; every rank ends up with the same bits.
  *   partial_buffers  host array of 2 * world device pointers, [parity * world + rank]: rank's partial
  *                    result of M * N floats (fp32, so that the sum is rounded to fp16 once) for calls
  *                    of that epoch parity, mapped into this process (symmetric memory); 16-byte aligned
- *   flag_arrays      host array of world device pointers: rank r's flag array of (M / 128) * 4 * world
+ *   flag_arrays      host array of world device pointers: rank r's flag array of at least 2 * world
  *                    32-bit words, zero before the first call, mapped into this process
  *   state            two 32-bit words of this rank's own device memory, zero before the first call and
  *                    used by this sequence of calls only (the epoch lives there, so the call can be
@@ -195,8 +195,8 @@ int spmm_b200_allreduce_partials_replayable(void*              stream,
  *                    next in the stream, does that (C is then not written by this call).
  *                    2: as 1, and the last block to finish also tells every rank that the partial rows
  *                    are complete; spmm_b200_allreduce_partials_f32_announced follows.  Measured on two
- *                    to eight B200s the two-launch form is the faster one: a system-scope fence at the
- *                    end of a kernel that keeps the memory system busy costs more than a launch.
+ *                    B200s the three forms take the same time within 1 % (the sum is bound by one
+ *                    system-scope fence, one flag over NVLink and one round trip for the loads).
  * world 1..8 (1 degenerates to a copy through the partial buffer); every rank must make the matching
  * call.  One process per GPU; the ranks must not share a GPU (each waits for the others). */
 int spmm_b200_spmm_row_parallel(void*        stream,
