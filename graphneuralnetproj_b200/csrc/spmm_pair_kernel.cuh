@@ -125,8 +125,8 @@ struct PendingSum {
 // NM  : pair MMAs per k step = 256-column blocks served by one restored tile (1 or 2); the cluster
 //       handles NM * 256 columns (blockIdx.y selects which)
 // D   : decoder warps (tile l of the chunk is restored by warp l % D into A buffer l % SA), each holding
-//       VPL 4-word vectors per lane -- the decode-size kernel's arrangement: eight independent warps keep
-//       enough loads in flight, four teams of two warps were measured 3 x slower per tile
+//       VPL 4-word vectors per lane -- the decode-size kernel's arrangement; with three to six decoders
+//       and more B buffers instead the kernel was measured 0-25 % slower
 // SA, SB: ring of A buffers and, separately, of B buffers (tile l uses B buffer l % SB): the B halves are
 //       NM times larger than a restored tile, so fewer of them fit
 //       p.sched partitions (M / 256) rows of tile pairs x (K / 64) among the clusters;
@@ -146,12 +146,12 @@ spmm_pair_kernel(const __grid_constant__ DecodeParams p)
     const uint32_t a_base    = smem_base;
     const uint32_t b_base    = a_base + SA * kATileBytes;
     const uint32_t bar_base  = b_base + SB * NM * BT::kBytes;
-    // barriers (8 bytes each): per A buffer "ready" -- the tile of that buffer is restored and its B half has landed
-    // (in the leader also: the partner's are) -- and "free" (the pair MMAs that read the buffer, and the B buffer of
-    // the same tile, have completed); then accumulators full x2, free x2 (leader's).  One wait and two commits per
-    // tile for the MMA lane: its time per tile, not the tensor core's, bounded an earlier form with more barriers.
-    // Both kinds form a ring of R = max(SA, SB) entries indexed by the tile (l % R): the decoder of tile l waits
-    // for the MMAs of tile l - SA (its A buffer), the loader for those of tile l - SB (its B buffer).
+    // barriers (8 bytes each): per tile "ready" (the leader's: both blocks' tiles are restored and both B halves
+    // have landed) and "done" (the pair MMAs that read the tile's A and B buffers have completed); then accumulators
+    // full x2, free x2 (leader's).  One wait and two commits per tile for the MMA lane: its time per tile, not the
+    // tensor core's, bounded an earlier form with more barriers.  Both kinds form a ring of R = max(SA, SB) entries
+    // indexed by the tile (l % R): the decoder of tile l waits for the MMAs of tile l - SA (its A buffer), the
+    // loader for those of tile l - SB (its B buffer).
     constexpr int R = SA > SB ? SA : SB;
     auto ready    = [&](int s) { return bar_base + 8u * s; };
     auto done     = [&](int s) { return bar_base + 8u * (R + s); };
