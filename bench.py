@@ -287,7 +287,9 @@ def run_ours(args):
     # (timing only)
     # "peera": as "peer", but the SpMM's last block flags the partial rows to the peers, so the exchange of flags
     # overlaps the launch of the reduction kernel
-    modes = ["none"] if world == 1 else (["peer", "peera", "peer2", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
+    # The main mode is the first of these that passes the check below: "peera" (1-1.5 % faster per step than "peer" on
+    # 2 and 4 GPUs), else "peer", ...
+    modes = ["none"] if world == 1 else (["peera", "peer", "peer2", "fused", "nccl", "none"] if peer_ok else ["nccl", "none"])
     main_mode = modes[0]
 
     def run_layer(L, copy, mode, use):
@@ -363,8 +365,8 @@ def run_ours(args):
     stream = torch.cuda.Stream()
     record = {}
     with torch.cuda.stream(stream):
-        # ---- every mode once, checked: a reduction whose bounded waits run out (2 s each) is dropped from the
-        # comparison instead of being timed launch after launch; the main mode has to work
+        # ---- every mode once, checked: a reduction whose bounded waits run out (2 s each) is dropped instead of being
+        # timed launch after launch, and the main mode becomes the first one left
         dropped = []
         for mode in list(modes):
             for L in layers:
@@ -372,12 +374,13 @@ def run_ours(args):
             torch.cuda.synchronize()
             failed = sp.device_status(reset=True) != 0 or sp.spmm_api.LIB.spmm_b200_allreduce_status(1) != 0
             if reduce_sum([1.0 if failed else 0.0])[0] > 0:
-                if mode == main_mode:
-                    raise RuntimeError("a bounded wait ran out in the main mode %r" % mode)
                 modes.remove(mode)
                 dropped.append(mode)
         if dropped:
             record["dropped_modes"] = dropped
+        if not modes or (world > 1 and modes[0] == "none"):
+            raise RuntimeError("no form of the sum over ranks passed its check: %r" % dropped)
+        main_mode = modes[0]
         # ---- warm-up, un-captured, through every mode
         for mode in modes:
             for i in range(warmup):
@@ -468,7 +471,7 @@ def run_ours(args):
         if not args.no_extras:
             # OPT-175B layer shapes sharded over the ranks: QKV and FFN1 by rows, FFN2 by K with the sum over ranks
             big = build(LAYERS_175B, 0x50, False)
-            if "peer" in modes:
+            if peer_ok:
                 add_peer_reducers(big)
             for mode in modes:
                 for L in big:
