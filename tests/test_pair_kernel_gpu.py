@@ -34,6 +34,7 @@ CASES = [  # M, K, N, sparsity, Split_K
     (2560, 4608, 512, 0.9, 4),   # 10 rows of pairs x 72 k tiles: split rows and whole rows
     (1024, 2048, 256, 1.0, 2),   # all tiles empty
     (768, 256, 512, 0.0, 2),     # fully dense tiles
+    (512, 256, 8192, 0.8, 1),    # the widest call: sixteen column blocks, more clusters than the device holds at once
 ]
 
 
@@ -100,6 +101,7 @@ TOKEN_MAJOR_CASES = [  # M, K, N, sparsity
     (2304, 1152, 512, 0.8),   # pairs of SMs, two MMAs per k step
     (1536, 640, 768, 0.5),    # three column blocks of 256
     (2560, 4608, 1024, 0.9),  # two column blocks of 512, split rows and whole rows
+    (768, 192, 4096, 0.8),    # eight column blocks of 512
 ]
 
 
