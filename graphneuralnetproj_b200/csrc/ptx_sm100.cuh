@@ -200,13 +200,6 @@ __device__ __forceinline__ void bulk_prefetch_l2(const void* src, uint32_t bytes
     asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(src), "r"(bytes) : "memory");
 }
 
-__device__ __forceinline__ uint4 ld_shared_128(uint32_t addr)
-{
-    uint4 v;
-    asm volatile("ld.shared.v4.u32 {%0, %1, %2, %3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-    return v;
-}
-
 // Streaming 128-bit load of read-only data that is used exactly once.
 __device__ __forceinline__ uint4 ld_stream_128(const uint4* p)
 {
@@ -215,38 +208,6 @@ __device__ __forceinline__ uint4 ld_stream_128(const uint4* p)
                  : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
                  : "l"(p));
     return v;
-}
-
-__device__ __forceinline__ void st_shared_u16(uint32_t addr, uint32_t value)
-{
-    asm volatile("st.shared.u16 [%0], %1;" ::"r"(addr), "h"(static_cast<uint16_t>(value)) : "memory");
-}
-
-// Scatter of one 4-word vector of tiled-CSL words: each word is value (low half) | position
-// (high half); the value goes to half-word `position` of the tile at shared address `tile`.
-__device__ __forceinline__ void scatter_words(uint32_t tile, const uint4& w)
-{
-    asm volatile("{\n\t"
-                 ".reg .b16 v0, v1, v2, v3, p0, p1, p2, p3;\n\t"
-                 ".reg .b32 a0, a1, a2, a3;\n\t"
-                 "mov.b32 {v0, p0}, %1;\n\t"
-                 "mov.b32 {v1, p1}, %2;\n\t"
-                 "mov.b32 {v2, p2}, %3;\n\t"
-                 "mov.b32 {v3, p3}, %4;\n\t"
-                 "mad.wide.u16 a0, p0, 2, %0;\n\t"
-                 "mad.wide.u16 a1, p1, 2, %0;\n\t"
-                 "mad.wide.u16 a2, p2, 2, %0;\n\t"
-                 "mad.wide.u16 a3, p3, 2, %0;\n\t"
-                 "st.shared.b16 [a0], v0;\n\t"
-                 "st.shared.b16 [a1], v1;\n\t"
-                 "st.shared.b16 [a2], v2;\n\t"
-                 "st.shared.b16 [a3], v3;\n\t"
-                 "}" ::"r"(tile),
-                 "r"(w.x),
-                 "r"(w.y),
-                 "r"(w.z),
-                 "r"(w.w)
-                 : "memory");
 }
 
 __device__ __forceinline__ void st_shared_zero_128(uint32_t addr)
